@@ -1,0 +1,399 @@
+"""Benchmark of the compressed-KV decode attention path (BASELINE.json metric).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload cfg2|cfg3|cfg4] [--ctx T] [--layers L]
+
+A *step* is one decode step: every layer appends one new (K, V) token to its
+8-bit stream and attends with one query token over
+[sink | compressed middle | window | stream].  Default workload (cfg2): one
+32768-token sequence on the Llama-3.1-8B geometry, 32 layers, synthetic K/V
+(rank-192 keys before RoPE, outlier-channel values), compressed by this
+package's own prefill compressor before the timed region.
+
+Metric: microseconds per sequence-layer-step (at one GPU and one sequence this is
+"us/step/layer").  With N > 1 GPUs each rank owns its own sequences (batch
+sharding, no data-path communication); the value is the aggregate
+ms_per_step / (layers * total sequences), time is the max over ranks.
+
+One JSON line is printed by rank 0.  `--impl reference` times the CPU port of the
+reference's algorithm (the numpy oracle) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+
+N_Q, N_KV, HD, RANK, SINK, WIN = 32, 8, 128, 192, 4, 64
+METRIC = "compressed_kv_decode_attn_us_per_step_per_layer"
+
+
+def algorithmic_bytes(n_comp, n_stream, rank=RANK, n_sink=SINK, n_win=WIN):
+    """Bytes one layer-step must touch, every operand counted once: packed int4
+    coefficients + VQ codes per middle token, fp16 basis, mean, scales, codebook,
+    fp16 sink/window K and V, stream codes + norms, query in, output out."""
+    per_tok = rank // 2 + N_KV * 32
+    fixed = 2 * rank * N_KV * HD + 2 * N_KV * HD + 2 * rank + 256 * 4 * 2 + 2 * N_KV * HD
+    fixed += (n_sink + n_win) * N_KV * HD * 2 * 2 + N_Q * HD * 2 * 2
+    return n_comp * per_tok + fixed + n_stream * (2 * N_KV * HD + 2 * 2 * N_KV)
+
+
+def measured_peaks():
+    path = os.path.join(HERE, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops_sustained", d.get("bf16_tflops", 0))), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while running."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    sm.append(float(parts[0]))
+                    mx.append(float(parts[1]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                      "sw_power_cap"), parts[3:7]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons),
+                       samples=len(sm))
+        return out
+
+
+# ----------------------------------------------------------------------------- reference arm / CPU baseline
+def synthetic_compressed_layer_numpy(n_comp, seed=0):
+    """A compressed layer with random codes (decode cost does not depend on code values)."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    p = N_KV * HD
+    nib = rng.integers(1, 16, size=(n_comp, RANK), dtype=np.uint8)
+    packed = (nib[:, 0::2] | (nib[:, 1::2] << 4)).astype(np.uint8).reshape(-1)
+    basis_q = rng.integers(-127, 128, size=(p, RANK)).astype(np.int8)
+    basis_scale = (0.08 / 127 * (0.5 + rng.random(RANK))).astype(np.float16)
+    mean = (rng.standard_normal(p) * 0.1).astype(np.float16)
+    return {
+        "k_coeffs": packed, "k_coeffs_shape": (n_comp, RANK),
+        "k_coeff_scale": (np.exp(-0.01 * np.arange(RANK)) * 0.4).astype(np.float16),
+        "k_basis_q": basis_q, "k_basis_scale": basis_scale,
+        "k_basis_f16": (basis_q.astype(np.float16) * basis_scale).astype(np.float16),
+        "k_mean": mean, "k_mean_f16": mean,
+        "v_indices_u8": rng.integers(0, 256, size=(N_KV, n_comp, 32)).astype(np.uint8),
+        "v_centroids_f16": (rng.standard_normal((256, 4)) * 0.4).astype(np.float16),
+        "v_ch_f16": (0.5 + rng.random((N_KV, HD)) * 3).astype(np.float16),
+        "sink_k": rng.standard_normal((N_KV, SINK, HD)).astype(np.float16),
+        "sink_v": rng.standard_normal((N_KV, SINK, HD)).astype(np.float16),
+        "win_k": rng.standard_normal((N_KV, WIN, HD)).astype(np.float16),
+        "win_v": rng.standard_normal((N_KV, WIN, HD)).astype(np.float16),
+        "n_compress": n_comp, "batch": 1, "compress_start": SINK,
+    }
+
+
+def time_cpu_port(n_comp, repeats, warmup, n_stream=8):
+    """Seconds per layer-step of the CPU port (numpy oracle) of the reference's decode,
+    including the stream append, on all host cores numpy's BLAS uses."""
+    import numpy as np
+    from oracle import shard_oracle as O
+    gc = synthetic_compressed_layer_numpy(n_comp)
+    inv = O.default_inv_freq()
+    cb = O.lloyd_max_codebook(HD, 8)
+    signs = O.stream_signs(0)
+    rng = np.random.default_rng(1)
+    sk = rng.standard_normal((n_stream, N_KV, HD)).astype(np.float16)
+    sv = rng.standard_normal((n_stream, N_KV, HD)).astype(np.float16)
+    ki, kn, vi, vn = O.stream_quantize(sk, sv, signs, cb)
+    times = []
+    for it in range(warmup + repeats):
+        q = rng.standard_normal((N_Q, HD)).astype(np.float16)
+        nk = rng.standard_normal((1, N_KV, HD)).astype(np.float16)
+        nv = rng.standard_normal((1, N_KV, HD)).astype(np.float16)
+        t0 = time.perf_counter()
+        a, b, c, d = O.stream_quantize(nk, nv, signs, cb)
+        stream = dict(k_idx=np.concatenate([ki, a]), v_idx=np.concatenate([vi, c]),
+                      k_norm=np.concatenate([kn, b]), v_norm=np.concatenate([vn, d]),
+                      signs=signs, codebook=cb)
+        O.fused_attention_compressed(q, gc, SINK + n_comp + WIN + n_stream, inv, stream=stream)
+        dt = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dt)
+    return sum(times) / len(times), os.cpu_count() or 1
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    T = args.ctx
+    n_comp = T - SINK - WIN
+    sec, cores = time_cpu_port(n_comp, max(1, args.steps), max(1, min(args.warmup, 1)))
+    us = sec * 1e6
+    sample = f"1 layer-step per timed step (of {args.layers} layers), n_comp={n_comp}, random codes, numpy"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": us, "unit": "us", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3 * args.layers,
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic",
+        "config": {"workload": f"cfg2: Llama-3.1-8B geometry, {T}-token context, {args.layers} layers, batch 1"},
+        "cpu_baseline": {"value": us, "unit": "us", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": us, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- our arm
+def build_cache(T, layers, seed0, dev):
+    import torch
+    from shard_b200 import Cache, synth
+    cache = Cache(num_layers=layers, rope_inv_freq=synth.rope_inv_freq())
+    cache._streaming = True
+    for li in range(layers):
+        k, v, _ = synth.make_kvq(T, seed0 + li, device=dev)
+        cache.layers[li].update(k, v)
+    cache.compress()
+    torch.cuda.synchronize()
+    return cache
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from shard_b200 import fused_attention_compressed
+    from shard_b200.parallel import BatchedDecoder
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    T, L = args.ctx, args.layers
+    n_comp = T - SINK - WIN
+    K, W = args.steps, max(args.warmup, 3)
+    seqs_per_gpu = args.seqs
+
+    t0 = time.perf_counter()
+    caches = [build_cache(T, L, 100 + 1000 * (rank * seqs_per_gpu + s), dev) for s in range(seqs_per_gpu)]
+    build_s = time.perf_counter() - t0
+    compress_s = sum(c.compress_seconds for c in caches) / len(caches)
+    ratio = caches[0].clean_compress_ratio()
+
+    bd = BatchedDecoder(caches, stream_capacity=2 * (K + W) + 8)
+    total = K + W
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    q_pool = torch.randn(total, L, seqs_per_gpu, N_Q, HD, generator=g, device=dev).half()
+    k_pool = torch.randn(total, L, seqs_per_gpu, N_KV, HD, generator=g, device=dev).half()
+    v_pool = torch.randn(total, L, seqs_per_gpu, N_KV, HD, generator=g, device=dev).half()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def one_step(j):
+        bd.q.copy_(q_pool[j])
+        bd.new_k.copy_(k_pool[j])
+        bd.new_v.copy_(v_pool[j])
+        bd.step(T + j)
+
+    # ---- device-resident timing -------------------------------------------------
+    for j in range(W):
+        one_step(j)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for j in range(W, W + K):
+        one_step(j)
+    ev1.record()
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+
+    # ---- dominant kernel: events around each decode_attn call (partial + combine) -----
+    import ctypes as C
+    from shard_b200 import _lib, ops
+    lib = _lib.load()
+    n_probe = min(K, 16)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+           for _ in range(n_probe * L)]
+    s_now = bd.n_stream
+    st = _lib.cur_stream()
+    for j in range(n_probe):
+        shape = bd._shape(T + j, s_now)
+        for li in range(L):
+            tab = bd.tables[li]
+            tptr = tab.data_ptr() if bd.S > 1 else C.addressof(tab)
+            a, b = evs[j * L + li]
+            a.record()
+            _lib.check(lib.shard_b200_decode_attn(tptr, bd.S, C.byref(shape), ops.ptr(bd.inv_freq),
+                                                  ops.ptr(bd.codebook), ops.ptr(bd.ws), bd.ws.numel(), st))
+            b.record()
+    torch.cuda.synchronize()
+    kern_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end through the public API, host buffers ----------------------------
+    e2e_steps = min(K, 32)
+    cache = caches[0]
+    hq = torch.randn(L, 1, N_Q, 1, HD).half().pin_memory()
+    hk = torch.randn(L, 1, N_KV, 1, HD).half().pin_memory()
+    hv = torch.randn(L, 1, N_KV, 1, HD).half().pin_memory()
+    hout = torch.empty(L, 1, N_Q, 1, HD, dtype=torch.float16).pin_memory()
+    dq = torch.empty_like(hq, device=dev)
+    dk = torch.empty_like(hk, device=dev)
+    dv = torch.empty_like(hv, device=dev)
+    dout = torch.empty_like(hout, device=dev)
+    inv = cache._rope_inv_freq
+
+    def e2e_step(pos):
+        dq.copy_(hq, non_blocking=True)
+        dk.copy_(hk, non_blocking=True)
+        dv.copy_(hv, non_blocking=True)
+        cache._fused_decode_update = True
+        for li in range(L):
+            layer = cache.layers[li]
+            layer.update(dk[li], dv[li])
+            dout[li] = fused_attention_compressed(dq[li], layer, pos, inv, None)
+        cache._fused_decode_update = False
+        hout.copy_(dout, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    pos = cache.layers[0].get_seq_length()
+    for j in range(3):
+        e2e_step(pos + j)
+    barrier()
+    t0 = time.perf_counter()
+    for j in range(e2e_steps):
+        e2e_step(pos + 3 + j)
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+
+    # ---- reduce over ranks ---------------------------------------------------------
+    vals = torch.tensor([ms_total, e2e_ms, kern_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms, kern_ms = (float(x) for x in vals.tolist())
+    ms_per_step = ms_total / K
+    n_seq_total = seqs_per_gpu * world
+    us = ms_per_step * 1e3 / (L * n_seq_total)
+
+    if rank == 0:
+        hbm_peak, tf_peak, peak_kind = measured_peaks()
+        s_mid = W + K // 2
+        bytes_ls = algorithmic_bytes(n_comp, s_mid)
+        flops_ls = 2 * n_comp * RANK * N_KV * HD + 4 * N_Q * HD * n_comp
+        kern_bytes = algorithmic_bytes(n_comp, s_now) * seqs_per_gpu
+        achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": us, "unit": "us", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {
+                "workload": f"cfg2: Llama-3.1-8B geometry ({N_Q}/{N_KV} heads, head_dim {HD}), {T}-token "
+                            f"context, {L} layers, {seqs_per_gpu} sequence(s) per GPU, 8-bit stream grows "
+                            f"{W}->{W + K} tokens",
+                "l2": "inputs larger than L2: one step touches %.0f MB of cache per GPU"
+                      % (bytes_ls * L * seqs_per_gpu / 1e6),
+                "parallelism": "batch-sharded, no communication" if world > 1 else "single GPU",
+            },
+            "hbm_gbs_per_gpu": bytes_ls * L * seqs_per_gpu / (ms_per_step * 1e-3) / 1e9,
+            "hbm_frac_of_8TBs": bytes_ls * L * seqs_per_gpu / (ms_per_step * 1e-3) / 8e12,
+            "tensor_tflops_per_gpu": flops_ls * L * seqs_per_gpu / (ms_per_step * 1e-3) / 1e12,
+            "decode_tokens_per_s": n_seq_total / (ms_per_step * 1e-3),
+            "prefill_compress_s_per_sequence": compress_s, "setup_s": build_s,
+            "clean_compress_ratio": ratio,
+            "roofline": {"kernel": "decode_partial_kernel + decode_combine_kernel (one decode_attn call)",
+                         "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": None,
+                         "us_per_launch": kern_ms * 1e3,
+                         "tensor_frac": (flops_ls * seqs_per_gpu / (kern_ms * 1e-3) / 1e12) / tf_peak},
+            "e2e": {"value": e2e_ms * 1e3 / L, "unit": "us",
+                    "h2d_bytes_per_step": L * (N_Q + 2 * N_KV) * HD * 2,
+                    "d2h_bytes_per_step": L * N_Q * HD * 2,
+                    "ms_per_step": e2e_ms, "api": "Cache.layers[i].update + fused_attention_compressed"},
+            "gpu_launches": K * (1 + 3 * L),
+            "clocks": clocks,
+        }
+        if args.cpu_baseline:
+            sec, cores = time_cpu_port(n_comp, 2, 1)
+            line["cpu_baseline"] = {"value": sec * 1e6, "unit": "us", "cores": cores, "kind": "port",
+                                    "sample": f"3 layer-steps (1 warm-up) of one layer, n_comp={n_comp}, "
+                                              "numpy port of the reference's CPU path"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ctx", type=int, default=32768)
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--seqs", type=int, default=1, help="sequences per GPU")
+    ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,227 @@
+/*
+ * shard_b200 -- C ABI of the B200 (sm_100a) compressed-KV attention kernels.
+ *
+ * The reference (bhengubv/shard) is pure Python: its device code is eight
+ * Triton kernels with PyTorch fallbacks and it has no foreign-function
+ * interface of its own.  Each entry point below therefore cites the Python
+ * function(s) of the reference whose work it replaces (paths relative to the
+ * reference project root).
+ *
+ * Conventions
+ *   - every pointer is a CUDA device pointer unless its name ends in _host;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = default stream);
+ *   - return value: 0 on success, a negative SHARD_E_* code on a rejected
+ *     argument, a positive value = cudaError_t of the failed runtime call;
+ *   - no entry point allocates or frees device memory; scratch space is passed
+ *     in by the caller (see the *_workspace_bytes helpers);
+ *   - kernels are asynchronous with respect to the host: they are enqueued on
+ *     `stream` and the call returns immediately;
+ *   - head_dim is 128 and the codebook has 256 entries of 4 channels
+ *     everywhere (Llama-3.1-8B geometry, the reference's defaults).
+ */
+#ifndef SHARD_B200_H_
+#define SHARD_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SHARD_OK 0
+#define SHARD_E_ARG (-1)       /* null pointer, bad size or unsupported geometry  */
+#define SHARD_E_WORKSPACE (-2) /* workspace too small                             */
+#define SHARD_E_ALIGN (-3)     /* pointer not aligned as documented               */
+
+#define SHARD_HEAD_DIM 128
+#define SHARD_PART_STRIDE 132  /* floats per (part, head) record: m, l, 0, 0, acc[128] */
+
+/* ABI version of this header; bumped on any signature change. */
+int shard_b200_abi_version(void);
+
+/* Human-readable text for a status code returned by any entry point. */
+const char* shard_b200_status_string(int status);
+
+/*
+ * Per-sequence tensor table of one layer's compressed cache: the device view of
+ * the dict the reference builds in Cache._build_gpu_format
+ * (src/shard/cache.py:406-460) plus the streamed-token buffers of
+ * CacheLayer._stream_append (src/shard/cache.py:193-241).
+ */
+typedef struct ShardSeq {
+  const uint8_t* k_coeffs;   /* [n_comp][rank/2]  packed int4 PCA coefficients          */
+  const void* k_wprep;       /* output of shard_b200_decode_prepare for this layer      */
+  const uint8_t* v_indices;  /* [nkv][n_comp][32] VQ codes                              */
+  const void* v_centroids;   /* fp16 [256][4]                                           */
+  const void* v_ch;          /* fp16 [nkv][128]   per-channel max-abs                   */
+  const void* sink_k;        /* fp16 [nkv][n_sink][128] (keys carry RoPE)               */
+  const void* sink_v;        /* fp16 [nkv][n_sink][128]                                 */
+  const void* win_k;         /* fp16 [nkv][n_win][128]                                  */
+  const void* win_v;         /* fp16 [nkv][n_win][128]                                  */
+  uint8_t* st_k_idx;         /* [cap][nkv][128]   8-bit Lloyd-Max codes of streamed K   */
+  uint8_t* st_v_idx;         /* [cap][nkv][128]                                         */
+  void* st_k_norm;           /* fp16 [cap][nkv]                                         */
+  void* st_v_norm;           /* fp16 [cap][nkv]                                         */
+  const float* signs;        /* [128] +-1, per layer                                    */
+  const void* phase;         /* fp16x2 [n_comp][64] (cos, sin) from shard_b200_phase_table */
+  const void* q;             /* fp16 [n_q][128]   query, RoPE applied at pos_q          */
+  void* out;                 /* fp16 [n_q][128] result, or fp32 [n_q][132] partial      */
+  const void* new_k;         /* fp16 [nkv][128]   token to append (stream_quantize)     */
+  const void* new_v;         /* fp16 [nkv][128]                                         */
+} ShardSeq;
+
+/* Scalars shared by every sequence of a launch. */
+typedef struct ShardDecodeShape {
+  int32_t n_q;            /* query heads (n_q / nkv must be 4)                           */
+  int32_t nkv;            /* KV heads                                                    */
+  int32_t rank;           /* PCA rank R: multiple of 32, 32..192                         */
+  int32_t n_comp;         /* tokens in the compressed middle segment                     */
+  int32_t tok_begin;      /* this call attends to middle tokens [tok_begin, tok_end)     */
+  int32_t tok_end;
+  int32_t n_sink;         /* fp16 sink tokens (0 to skip; sequence-split ranks > 0)      */
+  int32_t n_win;          /* fp16 window tokens                                          */
+  int32_t n_stream;       /* streamed tokens to attend to                                */
+  int32_t pos_q;          /* position of the query token                                 */
+  int32_t partial_out;    /* 0: out = fp16 attention; 1: out = fp32 (m, l, acc) partial  */
+  int32_t reserved;
+} ShardDecodeShape;
+
+/*
+ * cos/sin of fp32(compress_start + t - pos_q) * inv_freq[i], rounded to fp16, for
+ * t in [0, n_comp), i in [0, 64): the table of src/shard/attention.py:76-79.
+ * It depends only on positions, so one table serves every layer of a step.
+ * out: fp16x2 [n_comp][64], (cos, sin) interleaved.
+ */
+int shard_b200_phase_table(int32_t compress_start, int32_t pos_q, int32_t n_comp,
+                           const float* inv_freq, void* out, void* stream);
+
+/*
+ * Size in bytes of the prepared-weight blob for `nkv` KV heads and PCA rank `rank`.
+ */
+size_t shard_b200_wprep_bytes(int32_t nkv, int32_t rank);
+
+/*
+ * Folds k_coeff_scale into k_basis_f16, appends k_mean as one extra contraction
+ * column and lays the result out in tensor-core fragment order.  Runs once per
+ * layer after compression; replaces the per-step operand build of
+ * compressed_scores (src/shard/attention.py:34-63).
+ * basis_f16: [nkv*128][rank], coeff_scale: [rank], mean_f16: [nkv*128] (all fp16).
+ */
+int shard_b200_decode_prepare(const void* basis_f16, const void* coeff_scale, const void* mean_f16,
+                              int32_t nkv, int32_t rank, void* wprep_out, void* stream);
+
+/*
+ * Bytes of scratch shard_b200_decode_attn needs for `batch` sequences of this shape
+ * (0 if the shape is rejected).
+ */
+size_t shard_b200_decode_workspace_bytes(const ShardDecodeShape* shape_host, int32_t batch);
+
+/*
+ * Fused decode attention of one query token over
+ * [sink | compressed middle | window | streamed tokens]: replaces
+ * fused_attention_compressed (src/shard/attention.py:270-343) with its callees
+ * compressed_scores (18-81), int4_matmul (triton_kernels.py:65-88),
+ * _v_weighted_sum_compressed (83-121), vq_weighted_sum_all
+ * (triton_kernels.py:255-295), hadamard (cache.py:10-19) and
+ * CacheLayer._dequant_stream (cache.py:243-279).
+ *
+ * batch == 1: `seqs` is a HOST pointer to one ShardSeq (copied by value).
+ * batch  > 1: `seqs` is a DEVICE pointer to `batch` ShardSeq records describing
+ *             independent sequences that share `shape`.
+ * inv_freq: [64] fp32.  workspace: at least shard_b200_decode_workspace_bytes(shape, batch)
+ * bytes, 16-byte aligned; its contents need not be initialised and are overwritten.
+ * With shape.partial_out the result is the unnormalised per-head triple
+ * (max, sum-exp, acc[128]) in standard V space, ready for shard_b200_lse_merge.
+ */
+int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const ShardDecodeShape* shape_host,
+                           const float* inv_freq, const float* codebook, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
+/*
+ * Log-sum-exp combine of `n_parts` partials (fp32 [n_parts][n_q][132]) into fp16
+ * [n_q][128]: the mixing step of fused_attention_compressed_full
+ * (src/shard/attention.py:262-266), here used to merge the per-GPU partials of a
+ * sequence-split cache.  Parts are combined in index order.
+ */
+int shard_b200_lse_merge(const float* parts, int32_t n_parts, int32_t n_q, void* out_f16, void* stream);
+
+/*
+ * 8-bit Lloyd-Max quantisation of one new K and V token per KV head and append
+ * at row `slot` of the stream buffers: CacheLayer._stream_append
+ * (src/shard/cache.py:193-241) + quantize_per_token (src/shard/streaming.py:59-72).
+ * Uses new_k/new_v, signs and the st_* buffers of each ShardSeq.
+ * batch == 1: host pointer to one record; batch > 1: device pointer to a table.
+ * codebook: [256] fp32 ascending (Lloyd-Max centroids of N(0, 1/128)).
+ */
+int shard_b200_stream_quantize(const ShardSeq* seqs, int32_t batch, int32_t nkv, int32_t slot,
+                               const float* codebook, void* stream);
+
+/*
+ * fp16 K/V [nkv][n_stream][128] of the streamed tokens: CacheLayer._dequant_stream
+ * (src/shard/cache.py:243-279) + dequantize_per_token (streaming.py:74-79).  Used by
+ * the non-fused read path only.
+ */
+int shard_b200_stream_dequant(const uint8_t* idx, const void* norm_f16, const float* signs,
+                              const float* codebook, int32_t n_stream, int32_t nkv, void* out_f16,
+                              void* stream);
+
+/*
+ * Undo RoPE on prefill keys and flatten to [n][nkv*128] fp32 (column = kv*128+d):
+ * undo_rope (src/shard/rope.py:20-24) as called from Cache._compress_k
+ * (src/shard/cache.py:370-372).  k_f16: [nkv][.][128] with `tok_stride` elements
+ * between tokens' rows and `head_stride` elements between heads; token t has
+ * position pos_start + t.
+ */
+int shard_b200_undo_rope(const void* k_f16, int64_t head_stride, int64_t tok_stride, int32_t nkv,
+                         int32_t n, int32_t pos_start, const float* inv_freq, float* flat_out,
+                         void* stream);
+
+/*
+ * proj[n][keep] = (flat - mean) @ w, fp32: the PCA projection of
+ * Cache._compress_k (src/shard/cache.py:392).  flat: [n][dim], mean: [dim],
+ * w: [dim][keep] (= int8 basis * fp32 scale).  dim must be a multiple of 16.
+ */
+int shard_b200_k_project(const float* flat, const float* mean, const float* w, int32_t n, int32_t dim,
+                         int32_t keep, float* proj_out, void* stream);
+
+/* Scratch bytes for shard_b200_k_quantize_pack. */
+size_t shard_b200_k_quantize_workspace_bytes(int32_t n, int32_t keep);
+
+/*
+ * int4 codes of the projected keys: quantize_group -> dequantize_group
+ * (src/shard/rope.py:95-161) -> re-quantisation to [-7, 7]
+ * (src/shard/cache.py:416-419) -> int4_pack (triton_kernels.py:665-682).
+ * proj: [n][keep] fp32, alloc_bits: [keep] int32 in {0,2,4,6,8}, keep even.
+ * Outputs: coeff_scale fp32 [keep], packed [n*keep/2].
+ */
+int shard_b200_k_quantize_pack(const float* proj, const int32_t* alloc_bits, int32_t n, int32_t keep,
+                               float* coeff_scale_out, uint8_t* packed_out, void* workspace,
+                               size_t workspace_bytes, void* stream);
+
+/* Pairs adjacent int8 values in [-7, 7] into nibbles: int4_pack (triton_kernels.py:665-682). */
+int shard_b200_int4_pack(const int8_t* q, int64_t n_values, uint8_t* packed_out, void* stream);
+
+/*
+ * Hadamard rotation + per-channel max-abs normalisation of prefill values:
+ * Cache._compress_v (src/shard/cache.py:398-404) and the first half of vq_encode
+ * (cache.py:41-46).  v_f16: [nkv][.][128] with the given strides (elements).
+ * Outputs: x fp32 [nkv][n][128] (= rot / ch_max; viewed by the caller as
+ * [nkv*n*32][4] sub-vectors) and ch_max fp32 [nkv][128].
+ */
+int shard_b200_v_hadamard_normalise(const void* v_f16, int64_t head_stride, int64_t tok_stride,
+                                    int32_t nkv, int32_t n, float* x_out, float* ch_max_out,
+                                    void* stream);
+
+/*
+ * Nearest-centroid assignment, first minimum wins: vq_assign
+ * (triton_kernels.py:689-746).  x: [n][4] fp32, centroids: [256][4] fp32.
+ * Writes idx_u8 [n] and, if non-null, idx_i64 [n] (for the caller's centroid update).
+ */
+int shard_b200_vq_assign(const float* x, const float* centroids, int64_t n, uint8_t* idx_u8,
+                         int64_t* idx_i64, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SHARD_B200_H_ */

@@ -26,8 +26,12 @@ Conventions
 from __future__ import annotations
 
 import math
+import os
+from concurrent.futures import ThreadPoolExecutor
 
 import numpy as np
+
+HOST_THREADS = os.cpu_count() or 1
 
 F16 = np.float16
 F32 = np.float32
@@ -482,13 +486,18 @@ def compressed_scores(q_rope_f16, gc, pos_q, inv_freq, nkv=8):
 
     out = np.empty((n_q, n_comp), dtype=F32)
     coefs_t = np.ascontiguousarray(coefs.T)
-    for h in range(n_q):
+
+    def one_head(h):
         U = ((A[h].astype(F32) @ coefs_t).astype(F16) + a_mean[h][:, None]).astype(F16)  # (64, n_comp)
         V = ((Bm[h].astype(F32) @ coefs_t).astype(F16) + b_mean[h][:, None]).astype(F16)
         s1 = (U.astype(F32) * cos_t).sum(axis=0).astype(F16)
         s2 = (V.astype(F32) * sin_t).sum(axis=0).astype(F16)
         s = (s1 + s2).astype(F16)
         out[h] = (s.astype(F32) / F32(math.sqrt(hd))).astype(F16).astype(F32)
+
+    # heads are independent: spread them over the host cores (numpy releases the GIL)
+    with ThreadPoolExecutor(max_workers=HOST_THREADS) as pool:
+        list(pool.map(one_head, range(n_q)))
     return out
 
 

@@ -1,0 +1,165 @@
+"""Decode attention over a compressed cache + the Llama attention hook.
+
+`fused_attention_compressed` keeps the reference's signature
+(src/shard/attention.py:270-343) and returns the same tensor, but the whole
+computation -- scores on packed int4 PCA coefficients through the per-pair
+relative-phase RoPE identity, the fp16 sink/window segments, the 8-bit streamed
+tokens, one global softmax, the VQ-V weighted sum and the single inverse
+Hadamard -- is two kernel launches of libshard_b200.so.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib, ops
+from ._lib import ShardSeq, ptr
+from .streaming import get_codebook
+
+GQA = 4
+
+
+def _phase_for(cache, gc, pos_q, tok_begin, tok_end, dev):
+    """cos/sin table of the step; all layers of a step share positions, so it is
+    computed by the first layer that asks and reused by the others."""
+    key = (int(pos_q), gc["compress_start"], tok_begin, tok_end)
+    if cache._phase_key != key:
+        n = tok_end - tok_begin
+        if cache._phase is None or cache._phase.shape[0] < n:
+            cache._phase = torch.empty(max(n, 1), 64, 2, dtype=torch.float16, device=dev)
+        ops.phase_table(gc["compress_start"] + tok_begin, pos_q, n, cache._inv_freq(dev), out=cache._phase)
+        cache._phase_key = key
+    return cache._phase
+
+
+def _seq_record(gc, dev):
+    """ShardSeq of a layer: static pointers are filled once and cached in the dict."""
+    seq = gc.get("_seq")
+    if seq is None:
+        seq = ShardSeq()
+        seq.k_coeffs = ptr(gc["k_coeffs_kernel"])
+        seq.k_wprep = ptr(gc["k_wprep"])
+        seq.v_indices = ptr(gc["v_indices_u8"])
+        seq.v_centroids = ptr(gc["v_centroids_f16"])
+        seq.v_ch = ptr(gc["v_ch_f16"])
+        for name in ("sink_k", "sink_v", "win_k", "win_v"):
+            t = gc[name]
+            if not t.is_contiguous():
+                t = gc[name] = t.contiguous()
+            setattr(seq, name, ptr(t) if t.numel() else None)
+        gc["_seq"] = seq
+    if "k_idx_buf" in gc:
+        seq.st_k_idx, seq.st_v_idx = ptr(gc["k_idx_buf"]), ptr(gc["v_idx_buf"])
+        seq.st_k_norm, seq.st_v_norm = ptr(gc["k_norm_buf"]), ptr(gc["v_norm_buf"])
+        seq.signs = ptr(gc["signs"])
+    return seq
+
+
+def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_fp16_segments=True, out=None):
+    """Run the fused decode for one layer.
+
+    q_rope: (1, n_q, 1, 128) fp16 CUDA.  `tok_range` limits the middle segment to
+    [begin, end) (sequence-split mode); `partial_out` returns the fp32
+    (n_q, 132) record (max, sum-exp, 0, 0, acc[128]) instead of fp16 attention.
+    """
+    gc = layer._gpu_compressed
+    cache = layer._cache_ref
+    _lib.require_cuda(q_rope)
+    B, n_q, s_q, hd = q_rope.shape
+    nkv = cache._n_kv_heads
+    if B != 1 or s_q != 1:
+        raise NotImplementedError("decode kernel takes one query token of one sequence")
+    if hd != 128 or n_q != GQA * nkv:
+        raise NotImplementedError("decode kernel is built for head_dim 128 and 4 query heads per KV head")
+    if q_rope.dtype != torch.float16:
+        raise NotImplementedError("fp16 queries only")
+    if "decode_k" in gc:
+        raise NotImplementedError("fp16 decode buffer (non-streaming append) is served by the dequantised path")
+    dev = q_rope.device
+    n_comp = gc["n_compress"]
+    t0, t1 = (0, n_comp) if tok_range is None else tok_range
+    n_sink = gc["sink_k"].shape[2] if with_fp16_segments else 0
+    n_win = gc["win_k"].shape[2] if with_fp16_segments else 0
+    n_stream = gc.get("stream_n", 0) if with_fp16_segments else 0
+    seq = _seq_record(gc, dev)
+    q2 = q_rope.reshape(n_q, hd)
+    if not q2.is_contiguous():
+        q2 = q2.contiguous()
+    if out is None:
+        out = (torch.empty(n_q, _lib.PART_STRIDE, dtype=torch.float32, device=dev) if partial_out
+               else torch.empty(n_q, hd, dtype=torch.float16, device=dev))
+    seq.q, seq.out = ptr(q2), ptr(out)
+    seq.phase = ptr(_phase_for(cache, gc, pos_q, t0, t1, dev)) if t1 > t0 else None
+    shape = ops.make_shape(n_q, nkv, gc["k_rank_kernel"], n_comp, t0, t1, n_sink, n_win, n_stream, pos_q,
+                           partial_out)
+    need = ops.decode_workspace_bytes(shape, 1)
+    ws = cache._decode_ws
+    if ws is None or ws.numel() < need or ws.device != dev:
+        ws = cache._decode_ws = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+    cb = get_codebook(hd, 8, dev) if n_stream > 0 else None
+    ops.decode_attn(seq, 1, shape, cache._inv_freq(dev), cb, ws)
+    return out
+
+
+def fused_attention_compressed(q_rope, layer, pos_q, inv_freq=None, attn_mask=None):
+    """Attention of one query token over the layer's compressed cache; returns
+    (1, n_q, 1, hd) in q's dtype, or None if the layer is not compressed.
+
+    `attn_mask` is accepted for signature compatibility: for a single trailing
+    query of one sequence the causal mask is identically zero (the reference's own
+    fused variant skips it for the same reason, src/shard/attention.py:254).
+    `inv_freq` is taken from the cache the layer belongs to.
+    """
+    gc = getattr(layer, "_gpu_compressed", None)
+    if gc is None:
+        return None
+    if "decode_k" in gc:
+        return None
+    out = decode_layer(q_rope, layer, pos_q)
+    return out.view(1, q_rope.shape[1], 1, q_rope.shape[3])
+
+
+def enable_llama_fused_attention(model=None):
+    """Route LlamaAttention.forward through the fused decode kernel whenever the
+    cache is a compressed `shard_b200.Cache` and exactly one new token is processed
+    (reference: src/shard/attention.py:345-414).  Returns False if transformers'
+    Llama is unavailable."""
+    from .cache import Cache
+    try:
+        from transformers.models.llama import modeling_llama as ml
+    except ImportError:
+        return False
+    attn_cls = ml.LlamaAttention
+    if getattr(attn_cls, "_shard_b200_patched", False):
+        return True
+    stock_forward = attn_cls.forward
+
+    def forward(self, hidden_states, position_embeddings=None, attention_mask=None,
+                past_key_values=None, **kwargs):
+        cache = past_key_values
+        layer = cache.layers[self.layer_idx] if isinstance(cache, Cache) else None
+        use_fused = (layer is not None and layer._gpu_compressed is not None
+                     and hidden_states.shape[1] == 1 and hidden_states.shape[0] == 1
+                     and cache._rope_inv_freq is not None and cache._streaming)
+        if not use_fused:
+            return stock_forward(self, hidden_states, position_embeddings=position_embeddings,
+                                 attention_mask=attention_mask, past_key_values=past_key_values, **kwargs)
+        bsz, q_len = hidden_states.shape[:2]
+        shape = (bsz, q_len, -1, self.head_dim)
+        q = self.q_proj(hidden_states).view(shape).transpose(1, 2)
+        k = self.k_proj(hidden_states).view(shape).transpose(1, 2)
+        v = self.v_proj(hidden_states).view(shape).transpose(1, 2)
+        cos, sin = position_embeddings
+        q, k = ml.apply_rotary_pos_emb(q, k, cos, sin)
+        cache._fused_decode_update = True
+        try:
+            cache.update(k, v, self.layer_idx, {"sin": sin, "cos": cos})
+        finally:
+            cache._fused_decode_update = False
+        pos_q = layer.get_seq_length() - 1
+        out = fused_attention_compressed(q, layer, pos_q, cache._rope_inv_freq, attention_mask)
+        out = out.transpose(1, 2).reshape(bsz, q_len, -1)
+        return self.o_proj(out), None
+
+    attn_cls.forward = forward
+    attn_cls._shard_b200_patched = True
+    return True

@@ -1,0 +1,78 @@
+// Shared device helpers for the shard_b200 kernels (sm_100a).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/shard_b200.h"
+
+#define SHARD_CHECK_LAUNCH()                         \
+  do {                                               \
+    cudaError_t e__ = cudaGetLastError();            \
+    if (e__ != cudaSuccess) return (int)e__;         \
+  } while (0)
+
+namespace shard {
+
+constexpr int HD = 128;           // head_dim
+constexpr int HD2 = 64;           // rotary pairs per head
+constexpr int GQA = 4;            // query heads per KV head
+constexpr int VQ_GROUPS = 32;     // 4-channel sub-vectors per head vector
+constexpr int PART = SHARD_PART_STRIDE;
+// float(sqrt(128.0)) -- the divisor of the normalised Hadamard transform
+constexpr float SQRT_HD = 11.313708498984761f;
+constexpr float INV_SQRT_HD = 0.08838834764831845f;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
+
+// 128-point Walsh-Hadamard butterfly (no normalisation) over a warp where lane l
+// holds elements 4l..4l+3.  Stages run in the order h = 1, 2, 4, ..., 64 and each
+// output is a single fp32 add or subtract, so results are bit-identical to a
+// sequential stage-by-stage evaluation.
+__device__ __forceinline__ void fwht128_lane4(float (&x)[4], int lane) {
+  float a0 = __fadd_rn(x[0], x[1]), a1 = __fsub_rn(x[0], x[1]);
+  float a2 = __fadd_rn(x[2], x[3]), a3 = __fsub_rn(x[2], x[3]);
+  x[0] = __fadd_rn(a0, a2); x[2] = __fsub_rn(a0, a2);
+  x[1] = __fadd_rn(a1, a3); x[3] = __fsub_rn(a1, a3);
+#pragma unroll
+  for (int bit = 1; bit < 32; bit <<= 1) {
+    const bool upper = (lane & bit) != 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float other = __shfl_xor_sync(0xffffffffu, x[i], bit);
+      x[i] = upper ? __fsub_rn(other, x[i]) : __fadd_rn(x[i], other);
+    }
+  }
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Index of the nearest codebook entry as torch.bucketize + the reference's
+// strict left-neighbour test do it: idx = #entries < v (capped at n-1); the left
+// neighbour wins only if it is strictly closer.
+__device__ __forceinline__ int lloyd_max_code(float v, const float* __restrict__ cb, int n) {
+  int lo = 0, hi = n;
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if (cb[mid] < v) lo = mid + 1; else hi = mid;
+  }
+  int idx = lo < n - 1 ? lo : n - 1;
+  int left = idx > 0 ? idx - 1 : 0;
+  float dl = fabsf(__fsub_rn(cb[left], v));
+  float dr = fabsf(__fsub_rn(cb[idx], v));
+  return dl < dr ? left : idx;
+}
+
+}  // namespace shard

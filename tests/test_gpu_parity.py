@@ -1,0 +1,463 @@
+"""GPU parity tests: every call goes through the C ABI of libshard_b200.so and is
+compared with the numpy oracle and with fixtures produced by the reference.
+
+Bars: bit-exact for integer / byte outputs given identical inputs; decode attention
+within |x - ref| <= 2e-3 + 1e-2 |ref| of the reference's fp16 result, and much
+tighter against the float64 evaluation of the same compressed cache.
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import gc_from_golden, load_golden, tol_ok
+from oracle import shard_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    from shard_b200 import ops as _ops
+    return _ops
+
+
+def T(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+    return t if dtype is None else t.to(dtype)
+
+
+def N(t):
+    return t.detach().cpu().numpy()
+
+
+@pytest.fixture(scope="module")
+def codebook():
+    return T(O.lloyd_max_codebook(128, 8))
+
+
+# ------------------------------------------------------------------ stream quantizer
+def _quantize_tokens(ops, k, v, signs, codebook):
+    s, nkv, hd = k.shape
+    bufs = [torch.zeros(s, nkv, hd, dtype=torch.uint8, device=DEV) for _ in range(2)] + \
+           [torch.zeros(s, nkv, dtype=torch.float16, device=DEV) for _ in range(2)]
+    for t in range(s):
+        ops.stream_quantize(T(k[t]), T(v[t]), signs, codebook, bufs[0], bufs[1], bufs[2], bufs[3], t)
+    return bufs
+
+
+def test_stream_quantize_bit_exact(ops, codebook):
+    g = load_golden("stream.npz")
+    signs = T(g["signs"])
+    ki, vi, kn, vn = _quantize_tokens(ops, g["k"], g["v"], signs, codebook)
+    oki, okn, ovi, ovn = O.stream_quantize(g["k"], g["v"], g["signs"], O.lloyd_max_codebook(128, 8))
+    assert np.array_equal(N(ki), oki) and np.array_equal(N(vi), ovi)
+    assert np.array_equal(N(kn), okn) and np.array_equal(N(vn), ovn)
+    # against the reference's own codes: identical except where PyTorch's norm differs in the last ulp
+    assert np.mean(N(ki) != g["k_idx"]) < 1e-3 and np.mean(N(vi) != g["v_idx"]) < 1e-3
+
+
+def test_stream_quantize_matches_reference_run(ops, codebook, golden_cfg0):
+    g = golden_cfg0
+    k = g["st_k"][0].transpose(1, 0, 2)
+    v = g["st_v"][0].transpose(1, 0, 2)
+    ki, vi, kn, vn = _quantize_tokens(ops, k, v, T(g["st_signs"]), codebook)
+    assert np.array_equal(N(ki), g["st_k_idx"][:, 0]) and np.array_equal(N(vi), g["st_v_idx"][:, 0])
+    assert np.array_equal(N(kn), g["st_k_norm"][:, 0]) and np.array_equal(N(vn), g["st_v_norm"][:, 0])
+
+
+def test_stream_dequant_bit_exact(ops, codebook):
+    g = load_golden("stream.npz")
+    cb = O.lloyd_max_codebook(128, 8)
+    oki, okn, _, _ = O.stream_quantize(g["k"], g["v"], g["signs"], cb)
+    out = ops.stream_dequant(T(oki), T(okn), T(g["signs"]), codebook)
+    assert np.array_equal(N(out), O.dequant_stream(oki, okn, g["signs"], cb))
+
+
+def test_stream_zero_vector(ops, codebook):
+    k = np.zeros((1, 8, 128), np.float16)
+    ki, vi, kn, vn = _quantize_tokens(ops, k, k, T(O.stream_signs(0)), codebook)
+    oki, okn, _, _ = O.stream_quantize(k, k, O.stream_signs(0), O.lloyd_max_codebook(128, 8))
+    assert np.array_equal(N(ki), oki) and np.array_equal(N(kn), okn)
+
+
+# ------------------------------------------------------------------ K compressor
+def test_undo_rope(ops):
+    g = load_golden("rope_hadamard.npz")
+    inv_freq = T(O.default_inv_freq())
+    k = T(g["k"][0])
+    runs = [(0, 20, 4), (20, 30, 100000), (30, 40, 131000)]
+    for a, b, p0 in runs:
+        flat = ops.undo_rope(k[:, a:b, :], p0, inv_freq)                    # strided view
+        ref = g["undo"][0][:, a:b, :].transpose(1, 0, 2).reshape(b - a, -1)
+        assert np.allclose(N(flat), ref, atol=4e-6, rtol=0)
+
+
+def test_k_project(ops):
+    g = load_golden("kquant.npz")
+    w = (g["p_basis_q"].astype(np.float32) * g["p_scale"][None, :]).astype(np.float32)
+    proj = ops.k_project(T(g["p_flat"]), T(g["p_mean"]), T(w))
+    ref = O.project(g["p_flat"], g["p_mean"], g["p_basis_q"], g["p_scale"])
+    assert np.allclose(N(proj), ref, atol=2e-5, rtol=1e-5)
+    assert np.allclose(N(proj), g["p_proj"], atol=3e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("tag", ["a", "b", "c", "d"])
+def test_k_quantize_pack_bit_exact(ops, tag):
+    g = load_golden("kquant.npz")
+    packed, scale = ops.k_quantize_pack(T(g[f"{tag}_proj"]), g[f"{tag}_alloc"].tolist())
+    assert np.array_equal(N(scale), g[f"{tag}_scale"])
+    assert np.array_equal(N(packed), g[f"{tag}_packed"])
+
+
+def test_k_quantize_pack_chain512(ops, golden_chain512):
+    g = golden_chain512
+    packed, scale = ops.k_quantize_pack(T(g["proj"]), g["alloc"].tolist())
+    assert np.array_equal(N(packed), g["k_coeffs"])
+    assert np.array_equal(N(scale.half()), g["k_coeff_scale"])
+
+
+def test_int4_pack_bitwise(ops):
+    rng = np.random.default_rng(3)
+    for n in (1024 * 192, 7, 1):
+        q = rng.integers(-7, 8, size=n).astype(np.int8)
+        assert np.array_equal(N(ops.int4_pack(T(q))), O.int4_pack(q))
+
+
+# ------------------------------------------------------------------ V compressor
+def test_v_hadamard_normalise_bit_exact(ops):
+    g = load_golden("rope_hadamard.npz")
+    v = T(g["v"])
+    x, ch = ops.v_hadamard_normalise(v)
+    assert np.array_equal(N(ch), g["ch_max"])
+    assert np.array_equal(N(x), g["x"])
+    x2, ch2 = ops.v_hadamard_normalise(v[:, 3:29, :])                       # strided view
+    ox, _, och = O.v_rotate_normalise(g["v"][:, 3:29, :])
+    assert np.array_equal(N(ch2), och) and np.array_equal(N(x2), ox)
+
+
+def test_vq_assign_zero_mismatches(ops):
+    g = load_golden("vq.npz")
+    u8, i64 = ops.vq_assign(T(g["x"]), T(g["c"]))
+    assert np.array_equal(N(i64), g["idx"])          # the reference's cdist().argmin()
+    assert np.array_equal(N(u8).astype(np.int64), O.vq_assign(g["x"], g["c"]))
+    u8b, _ = ops.vq_assign(T(g["km_data"]), T(g["km_prev"]), want_i64=False)
+    assert np.array_equal(N(u8b).astype(np.int64), g["km_idx"])
+
+
+def test_vq_assign_ties_pick_first(ops):
+    c = np.zeros((256, 4), np.float32)
+    c[:, 0] = np.repeat(np.arange(128), 2)           # every centroid duplicated
+    x = np.stack([np.arange(0, 128, dtype=np.float32) + 0.25] + [np.zeros(128, np.float32)] * 3, 1)
+    u8, _ = ops.vq_assign(T(x), T(c))
+    assert np.array_equal(N(u8), (2 * np.arange(128)).astype(np.uint8))
+
+
+def test_kmeans_against_reference(ops):
+    from shard_b200.cache import kmeans
+    g = load_golden("vq.npz")
+    cent, idx = kmeans(T(g["km_data"]), 256, n_iter=30, init=T(g["km_init"]))
+    assert np.mean(N(idx).astype(np.int64) != g["km_idx"]) < 2e-3
+    assert np.allclose(N(cent), g["km_centroids"], atol=5e-3)
+
+
+# ------------------------------------------------------------------ decode attention
+def _decode(layer, q_np, pos_q, **kw):
+    from shard_b200.attention import decode_layer
+    q = T(q_np).view(1, q_np.shape[0], 1, 128)
+    return N(decode_layer(q, layer, pos_q, **kw))
+
+
+def test_decode_cfg0_against_reference(golden_cfg0):
+    from gpu_helpers import layer_from_golden
+    g = golden_cfg0
+    layer, gc_np = layer_from_golden(g)
+    q = g["q"][0, :, 0, :]
+    out = _decode(layer, q, int(g["pos_q"]))
+    assert tol_ok(out, g["out"][0, :, 0, :])                               # reference, default path
+    exact, *_ = O.attention_exact(q, gc_np, int(g["pos_q"]), O.default_inv_freq())
+    assert np.abs(out.astype(np.float64) - exact).max() < 1.5e-3           # fp16 output rounding dominates
+    assert tol_ok(out, exact, atol=1e-3, rtol=2e-3)
+
+
+def test_decode_chain512_against_reference(golden_chain512):
+    from gpu_helpers import layer_from_golden
+    g = golden_chain512
+    layer, gc_np = layer_from_golden(g)
+    out = _decode(layer, g["q"][0, :, 0, :], int(g["pos_q"]))
+    assert tol_ok(out, g["out"][0, :, 0, :])
+
+
+def test_decode_with_stream_against_reference(ops, codebook, golden_cfg0):
+    from gpu_helpers import layer_from_golden
+    g = golden_cfg0
+    layer, gc_np = layer_from_golden(g)
+    gc = layer._gpu_compressed
+    k = g["st_k"][0].transpose(1, 0, 2)
+    v = g["st_v"][0].transpose(1, 0, 2)
+    gc["signs"] = T(g["st_signs"])
+    gc["k_idx_buf"] = torch.zeros(16, 1, 8, 128, dtype=torch.uint8, device=DEV)
+    gc["v_idx_buf"] = torch.zeros(16, 1, 8, 128, dtype=torch.uint8, device=DEV)
+    gc["k_norm_buf"] = torch.zeros(16, 1, 8, dtype=torch.float16, device=DEV)
+    gc["v_norm_buf"] = torch.zeros(16, 1, 8, dtype=torch.float16, device=DEV)
+    cb = O.lloyd_max_codebook(128, 8)
+    for j in range(5):
+        ops.stream_quantize(T(k[j]), T(v[j]), gc["signs"], codebook, gc["k_idx_buf"], gc["v_idx_buf"],
+                            gc["k_norm_buf"], gc["v_norm_buf"], j)
+        gc["stream_n"] = j + 1
+        out = _decode(layer, g["st_q"][0, :, j, :], 2048 + j)
+        assert tol_ok(out, g["st_out"][0, :, j, :])
+        stream = dict(k_idx=g["st_k_idx"][:j + 1, 0], v_idx=g["st_v_idx"][:j + 1, 0],
+                      k_norm=g["st_k_norm"][:j + 1, 0], v_norm=g["st_v_norm"][:j + 1, 0],
+                      signs=g["st_signs"], codebook=cb)
+        exact, *_ = O.attention_exact(g["st_q"][0, :, j, :], gc_np, 2048 + j, O.default_inv_freq(), stream=stream)
+        assert tol_ok(out, exact, atol=1e-3, rtol=2e-3)
+
+
+def _check_random(n_comp, rank, n_sink, n_win, pos_q, compress_start=None, n_stream=0, seed=0, ops=None,
+                  codebook=None, atol=1e-3, rtol=3e-3):
+    from gpu_helpers import FakeCache, FakeLayer, gc_to_device, random_gc, random_query
+    gc_np = random_gc(n_comp, rank=rank, n_sink=n_sink, n_win=n_win, compress_start=compress_start, seed=seed)
+    inv = O.default_inv_freq()
+    layer = FakeLayer(gc_to_device(gc_np), FakeCache(torch.from_numpy(inv)))
+    stream = None
+    if n_stream:
+        rng = np.random.default_rng(seed + 5)
+        sk = rng.standard_normal((n_stream, 8, 128)).astype(np.float16)
+        sv = rng.standard_normal((n_stream, 8, 128)).astype(np.float16)
+        cb = O.lloyd_max_codebook(128, 8)
+        signs = O.stream_signs(3)
+        ki, kn, vi, vn = O.stream_quantize(sk, sv, signs, cb)
+        gc = layer._gpu_compressed
+        gc["signs"] = T(signs)
+        gc["k_idx_buf"], gc["v_idx_buf"] = T(ki[:, None]), T(vi[:, None])
+        gc["k_norm_buf"], gc["v_norm_buf"] = T(kn[:, None]), T(vn[:, None])
+        gc["stream_n"] = n_stream
+        stream = dict(k_idx=ki, v_idx=vi, k_norm=kn, v_norm=vn, signs=signs, codebook=cb)
+    q = random_query(seed=seed + 1)
+    out = _decode(layer, q, pos_q)
+    exact, *_ = O.attention_exact(q, gc_np, pos_q, inv, stream=stream)
+    assert np.isfinite(out).all()
+    assert tol_ok(out, exact, atol=atol, rtol=rtol), np.abs(out - exact).max()
+    return layer, gc_np, q, out
+
+
+@pytest.mark.parametrize("n_comp,rank,n_sink,n_win", [
+    (512, 192, 0, 0),        # the reference's own end-to-end test shape (no fp16 segments)
+    (1, 192, 4, 64),         # a single compressed token
+    (15, 64, 4, 64), (16, 128, 4, 64), (17, 32, 4, 64), (33, 160, 1, 3), (1000, 96, 4, 64),
+    (4097, 192, 4, 64),
+])
+def test_decode_ragged_shapes(n_comp, rank, n_sink, n_win):
+    _check_random(n_comp, rank, n_sink, n_win, pos_q=n_sink + n_comp + n_win + 32, seed=n_comp)
+
+
+def test_decode_odd_rank_is_padded():
+    """A kept rank that is not a multiple of 32 (short prompts) runs through the padded copy."""
+    layer, gc_np, _, _ = _check_random(187, 186, 4, 64, pos_q=300, seed=9)
+    assert layer._gpu_compressed["k_rank_kernel"] == 192 and "k_coeffs_padded" in layer._gpu_compressed
+
+
+def test_decode_far_positions():
+    """Query 131072 tokens past the window start: fp32 phase products of ~1e5 rad."""
+    _check_random(700, 192, 4, 64, pos_q=131072 + 700, compress_start=4, seed=4, atol=2e-3, rtol=1e-2)
+    _check_random(700, 192, 4, 64, pos_q=131072, compress_start=130000, seed=5, atol=2e-3, rtol=1e-2)
+
+
+def test_decode_stream_only_and_many_stream_tokens(ops, codebook):
+    _check_random(300, 192, 4, 64, pos_q=700, n_stream=70, seed=11)
+    _check_random(48, 192, 0, 0, pos_q=400, n_stream=255, seed=12)
+
+
+def test_decode_token_ranges_merge_to_whole(ops):
+    """Sequence-split on one GPU: partials of disjoint token ranges + lse_merge == whole."""
+    layer, gc_np, q, whole = _check_random(3000, 192, 4, 64, pos_q=3200, seed=21)
+    from shard_b200.parallel import split_ranges
+    for world in (2, 4, 8):
+        parts = []
+        for r, (b, e) in enumerate(split_ranges(3000, world)):
+            parts.append(T(_decode(layer, q, 3200, tok_range=(b, e), partial_out=True,
+                                   with_fp16_segments=(r == 0))))
+        merged = N(ops.lse_merge(torch.stack(parts)))
+        assert np.abs(merged.astype(np.float32) - whole.astype(np.float32)).max() <= 2e-3
+        exact, *_ = O.attention_exact(q, gc_np, 3200, O.default_inv_freq())
+        assert tol_ok(merged, exact, atol=1e-3, rtol=3e-3)
+
+
+def test_decode_sliced_layers_merge_to_whole(ops):
+    """Same, with each 'rank' holding only its slice of the coefficients and codes."""
+    from gpu_helpers import FakeLayer
+    from shard_b200.cache import attach_kernel_format
+    from shard_b200.parallel import shard_layer_tokens
+    layer, gc_np, q, whole = _check_random(2100, 192, 4, 64, pos_q=2300, seed=22)
+    parts = []
+    for r in range(3):
+        sub = shard_layer_tokens(layer._gpu_compressed, r, 3)
+        attach_kernel_format(sub, 8)
+        sl = FakeLayer(sub, layer._cache_ref)
+        layer._cache_ref._phase_key = None
+        parts.append(T(_decode(sl, q, 2300, partial_out=True, with_fp16_segments=(r == 0))))
+    merged = N(ops.lse_merge(torch.stack(parts)))
+    assert np.abs(merged.astype(np.float32) - whole.astype(np.float32)).max() <= 2e-3
+
+
+def test_decode_full_size_32k(ops):
+    """BASELINE configs[2] geometry (n_comp = 32700): compare with the float64 oracle and
+    check the size-independent partition property."""
+    layer, gc_np, q, whole = _check_random(32700, 192, 4, 64, pos_q=32768, seed=31)
+    a = T(_decode(layer, q, 32768, tok_range=(0, 16384), partial_out=True, with_fp16_segments=True))
+    b = T(_decode(layer, q, 32768, tok_range=(16384, 32700), partial_out=True, with_fp16_segments=False))
+    merged = N(ops.lse_merge(torch.stack([a, b])))
+    assert np.abs(merged.astype(np.float32) - whole.astype(np.float32)).max() <= 2e-3
+
+
+def test_decode_is_deterministic():
+    layer, gc_np, q, out = _check_random(5000, 192, 4, 64, pos_q=5100, seed=41)
+    again = _decode(layer, q, 5100)
+    assert np.array_equal(out, again)
+
+
+def test_batched_decoder_matches_single(ops, codebook):
+    """Three independent caches decoded by one launch per layer == one at a time."""
+    from gpu_helpers import FakeCache, FakeLayer, gc_to_device, random_gc, random_query
+    from shard_b200.parallel import BatchedDecoder
+
+    class C(FakeCache):
+        _num_layers = 2
+
+    inv = torch.from_numpy(O.default_inv_freq())
+    caches, gcs = [], []
+    for s in range(3):
+        c = C(inv)
+        c.layers = []
+        for li in range(2):
+            gc_np = random_gc(900, seed=100 + 10 * s + li)
+            gcs.append(gc_np)
+            c.layers.append(FakeLayer(gc_to_device(gc_np), c, li))
+        caches.append(c)
+    bd = BatchedDecoder(caches, stream_capacity=8)
+    rng = np.random.default_rng(7)
+    cb = O.lloyd_max_codebook(128, 8)
+    streams = {}
+    for step in range(3):
+        bd.q.copy_(T((rng.standard_normal(tuple(bd.q.shape))).astype(np.float16)))
+        bd.new_k.copy_(T(rng.standard_normal(tuple(bd.new_k.shape)).astype(np.float16)))
+        bd.new_v.copy_(T(rng.standard_normal(tuple(bd.new_v.shape)).astype(np.float16)))
+        pos_q = 968 + step
+        out = N(bd.step(pos_q))
+        for li in range(2):
+            for s in range(3):
+                signs = O.stream_signs(li)
+                ki, kn, vi, vn = O.stream_quantize(N(bd.new_k[li, s])[None], N(bd.new_v[li, s])[None], signs, cb)
+                st = streams.setdefault((li, s), dict(k_idx=[], v_idx=[], k_norm=[], v_norm=[]))
+                for key, val in zip(("k_idx", "k_norm", "v_idx", "v_norm"), (ki, kn, vi, vn)):
+                    st[key].append(val[0])
+                stream = {k: np.stack(v) for k, v in st.items()}
+                stream.update(signs=signs, codebook=cb)
+                exact, *_ = O.attention_exact(N(bd.q[li, s]), gcs[s * 2 + li], pos_q, O.default_inv_freq(),
+                                              stream=stream)
+                assert tol_ok(out[li, s], exact, atol=1e-3, rtol=3e-3)
+
+
+# ------------------------------------------------------------------ Cache end to end
+def test_cache_compress_and_decode_end_to_end(ops):
+    """Prefill -> compress() -> streamed decode steps through the public classes."""
+    from shard_b200 import Cache, fused_attention_compressed
+    from shard_b200 import synth
+    k, v, q = synth.make_kvq(1024, 5)
+    inv = synth.rope_inv_freq()
+    cache = Cache(num_layers=1, rope_inv_freq=inv)
+    cache._streaming = True
+    layer = cache.layers[0]
+    layer.update(k.to(DEV), v.to(DEV))
+    kt, vt, qt = synth.make_token(77)
+    cache._fused_decode_update = True
+    layer.update(kt.to(DEV), vt.to(DEV))                  # triggers compress(), appends to the stream
+    gc = layer._gpu_compressed
+    assert cache._compressed and gc["n_compress"] == 1024 - 68 and gc["stream_n"] == 1
+    n, keep = gc["k_coeffs_shape"]
+    assert keep == 192 and gc["k_coeffs"].numel() == n * keep // 2
+    assert gc["v_indices_u8"].shape == (8, n, 32) and gc["k_basis_q"].dtype == torch.int8
+    out = fused_attention_compressed(qt.to(DEV), layer, 1024, inv, None)
+    assert out.shape == (1, 32, 1, 128) and out.dtype == torch.float16
+    # oracle on the product's own dictionary
+    gc_np = {kk: (N(vv) if torch.is_tensor(vv) else vv) for kk, vv in gc.items() if not kk.startswith("_")}
+    for kk in ("sink_k", "sink_v", "win_k", "win_v"):
+        gc_np[kk] = gc_np[kk][0]
+    stream = dict(k_idx=N(gc["k_idx_buf"][:1, 0]), v_idx=N(gc["v_idx_buf"][:1, 0]),
+                  k_norm=N(gc["k_norm_buf"][:1, 0]), v_norm=N(gc["v_norm_buf"][:1, 0]),
+                  signs=N(gc["signs"]), codebook=O.lloyd_max_codebook(128, 8))
+    ref = O.fused_attention_compressed(N(qt)[0, :, 0, :], gc_np, 1024, O.default_inv_freq(), stream=stream)
+    assert tol_ok(N(out)[0, :, 0, :], ref)
+    # int4 codes of the product == oracle's double quantisation of the product's own projection
+    flat = ops.undo_rope(k.to(DEV)[0, :, 4:960, :], 4, inv.to(DEV))
+    w = (gc["k_basis_q"].float() * gc["k_basis_scale"].float()).contiguous()
+    proj = ops.k_project(flat, flat.mean(0).contiguous(), w)
+    qo, cs, _ = O.k_int4_codes(N(proj), gc["k_alloc"])
+    assert np.array_equal(O.int4_pack(qo), N(gc["k_coeffs"]))
+    # lossy-compression sanity against uncompressed attention
+    kk = torch.cat([k, kt], 2).float()[0].repeat_interleave(4, 0)
+    vv = torch.cat([v, vt], 2).float()[0].repeat_interleave(4, 0)
+    s = torch.einsum("hd,hnd->hn", qt.float()[0, :, 0], kk) / 128 ** 0.5
+    full = torch.einsum("hn,hnd->hd", torch.softmax(s, -1), vv)
+    err = (torch.from_numpy(N(out)[0, :, 0, :]).float() - full).abs().max().item()
+    assert err < 0.35 * full.abs().max().item()
+    # accounting formulas
+    assert cache.fp16_equivalent_bytes() == (1024 + 1) * 8 * 128 * 4
+    clean = sum(gc[x].numel() * gc[x].element_size() for x in
+                ("k_coeffs", "k_coeff_scale", "k_basis_q", "k_basis_scale", "k_mean", "v_packed",
+                 "sink_k", "sink_v", "win_k", "win_v")) + 8 * 128 * 2 + 256 * 4 * 2
+    assert cache.clean_memory_bytes() == clean
+    assert 5.0 < cache.clean_compress_ratio() < 12.0
+    # non-fused read path returns full-length fp16 K/V
+    cache._fused_decode_update = False
+    assert layer.keys.shape == (1, 8, 1025, 128) and layer.values.shape == (1, 8, 1025, 128)
+
+
+def test_cache_accounting_matches_reference_numbers(golden_chain512):
+    """Same tensors -> same storage bytes as the reference reports for its own cache."""
+    from gpu_helpers import layer_from_golden
+    from shard_b200 import Cache
+    g = golden_chain512
+    layer, _ = layer_from_golden(g)
+    cache = Cache(num_layers=1, rope_inv_freq=torch.from_numpy(O.default_inv_freq()))
+    gc = layer._gpu_compressed
+    gc["v_packed"] = gc["v_indices_u8"].view(-1)
+    gc["v_qdata"] = {"ch_maxabs": gc["v_ch_f16"].view(-1, 128), "centroids": gc["v_centroids_f16"]}
+    cache.layers[0]._gpu_compressed = gc
+    assert cache.clean_memory_bytes() == int(g["mem"][1])
+    assert cache.fp16_equivalent_bytes() == int(g["mem"][2])
+
+
+def test_llama_generate_with_fused_attention():
+    """model.generate(past_key_values=Cache) on a tiny random Llama with head_dim 128."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from shard_b200 import Cache, enable_llama_fused_attention
+    torch.manual_seed(0)
+    cfg = LlamaConfig(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=1, head_dim=128, vocab_size=512, rope_theta=500000.0,
+                      max_position_embeddings=4096)
+    model = LlamaForCausalLM(cfg).half().to(DEV).eval()
+    assert enable_llama_fused_attention(model)
+    ids = torch.randint(0, 512, (1, 300), generator=torch.Generator().manual_seed(1)).to(DEV)
+    cache = Cache.from_model(model)
+    cache._streaming = True
+    with torch.no_grad():
+        out = model.generate(ids, max_new_tokens=8, do_sample=False, past_key_values=cache, pad_token_id=0)
+        ref = model.generate(ids, max_new_tokens=8, do_sample=False, pad_token_id=0)
+    assert out.shape == (1, 308)
+    assert cache._compressed and cache.layers[1]._gpu_compressed["stream_n"] >= 7
+    assert cache.compress_ratio() > 1.0
+    # logits of one more step: compressed cache vs. uncompressed run stay close
+    with torch.no_grad():
+        full = model(ref[:, :-1]).logits[0, -1].float()
+        cache2 = Cache.from_model(model)
+        cache2._streaming = True
+        model(ids, past_key_values=cache2, use_cache=True)
+        nxt = model(ref[:, 300:301], past_key_values=cache2, use_cache=True).logits[0, -1].float()
+        want = model(ref[:, :301]).logits[0, -1].float()
+    assert torch.isfinite(nxt).all() and torch.isfinite(full).all()
+    assert (nxt - want).abs().max().item() < 0.25 * want.abs().max().item() + 0.05
