@@ -201,6 +201,7 @@ def build_cache(T, layers, seed0, dev):
         cache.layers[li].update(k, v)
     cache.compress()
     torch.cuda.synchronize()
+    torch.cuda.empty_cache()
     return cache
 
 

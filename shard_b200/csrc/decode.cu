@@ -18,47 +18,61 @@
 // 16 tokens for one KV head as a [16 x R] x [R x 128] tensor-core product straight from
 // the packed int4 coefficients (nibbles are expanded to fp16 in registers), rotates
 // them by the relative phase, and dots them with the un-rotated query.
-#include "common.cuh"
+#include <cstdlib>
+
+#include "decode_common.cuh"
 
 namespace shard {
 
 constexpr int DEC_THREADS = 128;
 constexpr int DEC_WARPS = 4;
-constexpr int TILE_TOK = 16;           // tokens per warp tile (mma M)
-constexpr int STREAM_TOK_PER_CTA = 32;
-constexpr int CTA_SLOTS = 148 * 3;     // resident decode CTAs on a B200 (148 SMs x 3)
+constexpr int TILE_TOK = 16;           // tokens per warp tile of the mma.sync kernel
+constexpr int MMA_CTA_SLOTS = 148 * 3; // resident CTAs of the mma.sync kernel on a B200
+constexpr int TC_TILE_TOK = 128;       // tokens per CTA tile of the tcgen05 kernel
+constexpr int TC_CTA_SLOTS = 148 * 2;  // two resident CTAs per SM
+constexpr int WS_HEADER_BYTES = 16;    // status word + padding in front of the partial records
 
-struct DecodeParams {
-  ShardSeq one;
-  const ShardSeq* table;
-  ShardDecodeShape sh;
-  const float* inv_freq;
-  const float* codebook;
-  float* ws;
-  int n_chunks;
-  int tiles_per_chunk;
-  int n_fp16_ctas;
-  int n_stream_ctas;
-  int n_parts;
-};
+// implemented in decode_tc.cu
+size_t tc_wprep_bytes(int nkv, int rank);
+int launch_prepare_tc(const void* basis, const void* cscale, const void* mean, int nkv, int rank, void* out,
+                      cudaStream_t st);
+int launch_partial_tc(const DecodeParams& p, dim3 grid, cudaStream_t st);
+
+__host__ __device__ inline size_t tc_blob_bytes(int nkv, int rank) {
+  return (size_t)nkv * (((rank + 63) / 64) * 16384 + 512);
+}
 
 struct DecodePlan {
   int n_chunks, tiles_per_chunk, n_fp16_ctas, n_stream_ctas, n_parts;
 };
 
+// Which kernel walks the compressed middle: the tcgen05 kernel (default) or the older
+// mma.sync kernel, kept for A/B timing (environment SHARD_B200_DECODE=mma).
+static bool use_tc() {
+  static int mode = -1;
+  if (mode < 0) {
+    const char* e = getenv("SHARD_B200_DECODE");
+    mode = (e && e[0] == 'm') ? 0 : 1;
+  }
+  return mode == 1;
+}
+
 static DecodePlan make_plan(const ShardDecodeShape& sh, int batch) {
   DecodePlan pl{};
+  const bool tc = use_tc();
+  const int tile_tok = tc ? TC_TILE_TOK : TILE_TOK;
+  const int slots = tc ? TC_CTA_SLOTS : MMA_CTA_SLOTS;
   const int n_tok = sh.tok_end - sh.tok_begin;
-  const int n_tiles = (n_tok + TILE_TOK - 1) / TILE_TOK;
+  const int n_tiles = (n_tok + tile_tok - 1) / tile_tok;
   if (n_tiles > 0) {
     const int groups = sh.nkv * batch;
     int tpc;
-    if (groups >= CTA_SLOTS / 2) {
-      tpc = 64;
+    if (groups >= slots / 2) {
+      tpc = tc ? 8 : 64;
     } else {
-      const int chunks = CTA_SLOTS / groups;
+      const int chunks = slots / groups;
       tpc = (n_tiles + chunks - 1) / chunks;
-      if (tpc < DEC_WARPS) tpc = DEC_WARPS;
+      if (!tc && tpc < DEC_WARPS) tpc = DEC_WARPS;
     }
     pl.tiles_per_chunk = tpc;
     pl.n_chunks = (n_tiles + tpc - 1) / tpc;
@@ -72,8 +86,9 @@ static DecodePlan make_plan(const ShardDecodeShape& sh, int batch) {
 // ---------------------------------------------------------------------------
 // phase table
 // ---------------------------------------------------------------------------
+// row t of the table: 64 fp16 cosines (pairs 0..63) followed by 64 fp16 sines
 __global__ void __launch_bounds__(256) phase_table_kernel(int delta0, int n, const float* __restrict__ inv_freq,
-                                                          __half2* __restrict__ out) {
+                                                          __half* __restrict__ out) {
   const size_t total = (size_t)n * HD2;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
@@ -81,7 +96,8 @@ __global__ void __launch_bounds__(256) phase_table_kernel(int delta0, int n, con
     const float phase = __fmul_rn((float)(delta0 + t), inv_freq[i]);
     float sn, cs;
     sincosf(phase, &sn, &cs);
-    out[idx] = __halves2half2(__float2half_rn(cs), __float2half_rn(sn));
+    out[(size_t)t * HD + i] = __float2half_rn(cs);
+    out[(size_t)t * HD + HD2 + i] = __float2half_rn(sn);
   }
 }
 
@@ -145,54 +161,6 @@ __device__ __forceinline__ uint32_t nib2half2(uint32_t y) {
   return *reinterpret_cast<const uint32_t*>(&r);
 }
 
-struct SoftmaxState {
-  float m[GQA];
-  float l[GQA];       // lane-local partial sums (see call sites)
-  float acc[GQA][4];  // lane owns channels 4*lane .. 4*lane+3
-};
-
-__device__ __forceinline__ void softmax_init(SoftmaxState& st) {
-#pragma unroll
-  for (int h = 0; h < GQA; ++h) {
-    st.m[h] = neg_inf();
-    st.l[h] = 0.f;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) st.acc[h][c] = 0.f;
-  }
-}
-
-// one streamed token: fp16 value of channels 4*lane..+3 exactly as the reference's
-// dequantize_per_token + norm scaling produce it
-__device__ __forceinline__ void stream_dequant_lane4(const uint8_t* __restrict__ idx_row, float nrm,
-                                                     const float* __restrict__ cbs, const float4 sg, int lane,
-                                                     float (&o)[4]) {
-  const uint32_t codes = *reinterpret_cast<const uint32_t*>(idx_row + 4 * lane);
-  float x[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) x[i] = cbs[(codes >> (8 * i)) & 0xff];
-  fwht128_lane4(x, lane);
-  const float sgn[4] = {sg.x, sg.y, sg.z, sg.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __half unit = __float2half_rn(__fmul_rn(__fdiv_rn(x[i], SQRT_HD), sgn[i]));
-    o[i] = __half2float(__float2half_rn(__fmul_rn(__half2float(unit), nrm)));
-  }
-}
-
-// online-softmax update with one token whose 4 scores are warp-uniform
-__device__ __forceinline__ void row_update(SoftmaxState& st, const float (&s)[GQA], const float (&v)[4]) {
-#pragma unroll
-  for (int h = 0; h < GQA; ++h) {
-    const float mn = fmaxf(st.m[h], s[h]);
-    const float alpha = (st.m[h] == neg_inf()) ? 0.f : exp2f((st.m[h] - mn) * LOG2E);
-    const float pr = exp2f((s[h] - mn) * LOG2E);
-    st.m[h] = mn;
-    st.l[h] = st.l[h] * alpha + pr;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) st.acc[h][c] = st.acc[h][c] * alpha + pr * v[c];
-  }
-}
-
 // ---------------------------------------------------------------------------
 // split-KV pass
 // ---------------------------------------------------------------------------
@@ -222,7 +190,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) decode_partial_kernel(const __
   // ---- stage per-CTA constants -------------------------------------------
   if (is_mid) {
     const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(sq.k_wprep) +
-                                                      (size_t)kv * W_BYTES);
+                                                      tc_blob_bytes(sh.nkv, R) + (size_t)kv * W_BYTES);
     uint4* dst = reinterpret_cast<uint4*>(smem);
     for (int i = tid; i < W_BYTES / 16; i += DEC_THREADS) dst[i] = src[i];
     const uint2* cb_src = reinterpret_cast<const uint2*>(sq.v_centroids);
@@ -230,24 +198,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) decode_partial_kernel(const __
   } else if (!is_fp16) {
     for (int i = tid; i < 256; i += DEC_THREADS) cbs[i] = p.codebook[i];
   }
-  {
-    // query: thread d handles channel d of the 4 heads of this KV group
-    const int d = tid, i = d & 63;
-    const float phase = __fmul_rn((float)sh.pos_q, p.inv_freq[i]);
-    float sn, cs;
-    sincosf(phase, &sn, &cs);
-    const __half c16 = __float2half_rn(cs), s16 = __float2half_rn(sn);
-    const __half* qg = reinterpret_cast<const __half*>(sq.q) + (size_t)kv * GQA * HD;
-#pragma unroll
-    for (int h = 0; h < GQA; ++h) {
-      const __half x = qg[h * HD + d];
-      const __half other = qg[h * HD + (d ^ 64)];
-      const __half rot = (d < 64) ? __hneg(other) : other;
-      const __half un = __hsub(__hmul(x, c16), __hmul(rot, s16));
-      qn[h * HD + d] = __half2float(un);
-      qr[h * HD + d] = __half2float(x);
-    }
-  }
+  stage_query(sq, kv, sh.pos_q, p.inv_freq, tid, qn, qr);
   __syncthreads();
 
   SoftmaxState st;
@@ -319,13 +270,12 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) decode_partial_kernel(const __
 
       // rotate by the relative phase and dot with the un-rotated query
       float sA[GQA] = {0.f, 0.f, 0.f, 0.f}, sB[GQA] = {0.f, 0.f, 0.f, 0.f};
-      const __half2* phA = phase_tab + (size_t)(tAc - sh.tok_begin) * HD2 + 2 * qd;
-      const __half2* phB = phase_tab + (size_t)(tBc - sh.tok_begin) * HD2 + 2 * qd;
+      const __half2* phA = phase_tab + (size_t)(tAc - sh.tok_begin) * HD2 + qd;   // cos pairs; sines 32 further
+      const __half2* phB = phase_tab + (size_t)(tBc - sh.tok_begin) * HD2 + qd;
 #pragma unroll
       for (int ntp = 0; ntp < 8; ++ntp) {
-        const uint2 rawA = *reinterpret_cast<const uint2*>(phA + 8 * ntp);
-        const uint2 rawB = *reinterpret_cast<const uint2*>(phB + 8 * ntp);
-        const uint32_t pa[2] = {rawA.x, rawA.y}, pb[2] = {rawB.x, rawB.y};
+        const float2 cosA = __half22float2(phA[4 * ntp]), sinA = __half22float2(phA[32 + 4 * ntp]);
+        const float2 cosB = __half22float2(phB[4 * ntp]), sinB = __half22float2(phB[32 + 4 * ntp]);
         float2 qa[GQA], qb[GQA];
 #pragma unroll
         for (int h = 0; h < GQA; ++h) {
@@ -334,8 +284,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) decode_partial_kernel(const __
         }
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const float2 csA = __half22float2(*reinterpret_cast<const __half2*>(&pa[e]));
-          const float2 csB = __half22float2(*reinterpret_cast<const __half2*>(&pb[e]));
+          const float2 csA = e ? make_float2(cosA.y, sinA.y) : make_float2(cosA.x, sinA.x);
+          const float2 csB = e ? make_float2(cosB.y, sinB.y) : make_float2(cosB.x, sinB.x);
           const float cA = acc[ntp][e], dA = acc[ntp + 8][e];
           const float cB = acc[ntp][2 + e], dB = acc[ntp + 8][2 + e];
           const float crA = cA * csA.x - dA * csA.y, drA = dA * csA.x + cA * csA.y;
@@ -415,92 +365,18 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) decode_partial_kernel(const __
       st.acc[h][0] *= ch01.x; st.acc[h][1] *= ch01.y; st.acc[h][2] *= ch23.x; st.acc[h][3] *= ch23.y;
     }
   } else {
-    // ---- fp16 rows: sink + window, or streamed tokens (one warp per token) ----
-    int u_lo, u_hi;
-    if (is_fp16) { u_lo = 0; u_hi = sh.n_sink + sh.n_win; }
-    else {
-      const int j = part - p.n_chunks - p.n_fp16_ctas;
-      u_lo = j * STREAM_TOK_PER_CTA;
+    int u_lo = 0, u_hi = sh.n_sink + sh.n_win;
+    if (!is_fp16) {
+      u_lo = (part - p.n_chunks - p.n_fp16_ctas) * STREAM_TOK_PER_CTA;
       u_hi = min(u_lo + STREAM_TOK_PER_CTA, sh.n_stream);
     }
-    float4 sg = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (!is_fp16) sg = *reinterpret_cast<const float4*>(sq.signs + 4 * lane);
-    float4 qv[GQA];
-#pragma unroll
-    for (int h = 0; h < GQA; ++h) qv[h] = *reinterpret_cast<const float4*>(qr + h * HD + 4 * lane);
-
-    for (int u = u_lo + warp; u < u_hi; u += DEC_WARPS) {
-      float kx[4], vx[4];
-      if (is_fp16) {
-        const bool in_sink = u < sh.n_sink;
-        const int r = in_sink ? u : u - sh.n_sink;
-        const int rows = in_sink ? sh.n_sink : sh.n_win;
-        const __half* kb = reinterpret_cast<const __half*>(in_sink ? sq.sink_k : sq.win_k);
-        const __half* vb = reinterpret_cast<const __half*>(in_sink ? sq.sink_v : sq.win_v);
-        const size_t off = ((size_t)kv * rows + r) * HD + 4 * lane;
-        const uint2 kr = *reinterpret_cast<const uint2*>(kb + off);
-        const uint2 vr = *reinterpret_cast<const uint2*>(vb + off);
-        const float2 k01 = __half22float2(*reinterpret_cast<const __half2*>(&kr.x));
-        const float2 k23 = __half22float2(*reinterpret_cast<const __half2*>(&kr.y));
-        const float2 v01 = __half22float2(*reinterpret_cast<const __half2*>(&vr.x));
-        const float2 v23 = __half22float2(*reinterpret_cast<const __half2*>(&vr.y));
-        kx[0] = k01.x; kx[1] = k01.y; kx[2] = k23.x; kx[3] = k23.y;
-        vx[0] = v01.x; vx[1] = v01.y; vx[2] = v23.x; vx[3] = v23.y;
-      } else {
-        const size_t row = (size_t)u * sh.nkv + kv;
-        const float kn = __half2float(reinterpret_cast<const __half*>(sq.st_k_norm)[row]);
-        const float vn = __half2float(reinterpret_cast<const __half*>(sq.st_v_norm)[row]);
-        stream_dequant_lane4(sq.st_k_idx + row * HD, kn, cbs, sg, lane, kx);
-        stream_dequant_lane4(sq.st_v_idx + row * HD, vn, cbs, sg, lane, vx);
-      }
-      float s[GQA];
-#pragma unroll
-      for (int h = 0; h < GQA; ++h) {
-        float d = qv[h].x * kx[0];
-        d = fmaf(qv[h].y, kx[1], d);
-        d = fmaf(qv[h].z, kx[2], d);
-        d = fmaf(qv[h].w, kx[3], d);
-        s[h] = warp_sum(d) * INV_SQRT_HD;
-      }
-      row_update(st, s, vx);
-    }
+    process_rows<DEC_WARPS>(st, sq, sh, kv, is_fp16, u_lo, u_hi, qr, cbs, warp, lane);
   }
 
   // ---- merge the 4 warps and emit this CTA's partial -------------------------
   __syncthreads();  // all reads of the W fragments are done; reuse that space
-  float* mw = reinterpret_cast<float*>(smem);       // [4 warps][4 heads] max
-  float* lw = mw + DEC_WARPS * GQA;                 // [4 warps][4 heads] sum-exp
-  float* aw = lw + DEC_WARPS * GQA;                 // [4 warps][4 heads][128]
-  if (lane == 0) {
-#pragma unroll
-    for (int h = 0; h < GQA; ++h) { mw[warp * GQA + h] = st.m[h]; lw[warp * GQA + h] = st.l[h]; }
-  }
-#pragma unroll
-  for (int h = 0; h < GQA; ++h)
-    *reinterpret_cast<float4*>(aw + (warp * GQA + h) * HD + 4 * lane) =
-        make_float4(st.acc[h][0], st.acc[h][1], st.acc[h][2], st.acc[h][3]);
-  __syncthreads();
-  {
-    const int d = tid;
-    float* rec_base = p.ws + (((size_t)blockIdx.z * p.n_parts + part) * sh.n_q + (size_t)kv * GQA) * PART;
-#pragma unroll
-    for (int h = 0; h < GQA; ++h) {
-      float M = neg_inf();
-#pragma unroll
-      for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, mw[w * GQA + h]);
-      float L = 0.f, a = 0.f;
-#pragma unroll
-      for (int w = 0; w < DEC_WARPS; ++w) {
-        const float mwv = mw[w * GQA + h];
-        const float wt = (mwv == neg_inf()) ? 0.f : exp2f((mwv - M) * LOG2E);
-        L = fmaf(wt, lw[w * GQA + h], L);
-        a = fmaf(wt, aw[(w * GQA + h) * HD + d], a);
-      }
-      float* rec = rec_base + h * PART;
-      if (d == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
-      rec[4 + d] = a;
-    }
-  }
+  float* rec_base = p.ws + (((size_t)blockIdx.z * p.n_parts + part) * sh.n_q + (size_t)kv * GQA) * PART;
+  emit_partial<DEC_WARPS>(st, reinterpret_cast<float*>(smem), rec_base, tid, warp, lane);
 }
 
 // ---------------------------------------------------------------------------
@@ -581,14 +457,17 @@ extern "C" int shard_b200_phase_table(int32_t compress_start, int32_t pos_q, int
   const size_t total = (size_t)n_comp * HD2;
   const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
   phase_table_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(compress_start - pos_q, n_comp, inv_freq,
-                                                                (__half2*)out);
+                                                                (__half*)out);
   SHARD_CHECK_LAUNCH();
   return SHARD_OK;
 }
 
+// blob = [tcgen05 layout: nkv x (W core matrices + fp32 mean)] [mma.sync fragment layout]
+static size_t mma_wprep_bytes(int nkv, int rank) { return (size_t)nkv * (rank / 16 + 1) * 16 * 32 * 8; }
+
 extern "C" size_t shard_b200_wprep_bytes(int32_t nkv, int32_t rank) {
   if (nkv < 1 || rank < 32 || rank > 192 || (rank % 32)) return 0;
-  return (size_t)nkv * (rank / 16 + 1) * 16 * 32 * 8;
+  return tc_wprep_bytes(nkv, rank) + mma_wprep_bytes(nkv, rank);
 }
 
 extern "C" int shard_b200_decode_prepare(const void* basis_f16, const void* coeff_scale, const void* mean_f16,
@@ -596,9 +475,11 @@ extern "C" int shard_b200_decode_prepare(const void* basis_f16, const void* coef
   if (!basis_f16 || !coeff_scale || !mean_f16 || !wprep_out) return SHARD_E_ARG;
   if (nkv < 1 || rank < 32 || rank > 192 || (rank % 32)) return SHARD_E_ARG;
   if ((uintptr_t)wprep_out & 15) return SHARD_E_ALIGN;
+  launch_prepare_tc(basis_f16, coeff_scale, mean_f16, nkv, rank, wprep_out, (cudaStream_t)stream);
   const int total = nkv * (rank / 16 + 1) * 16 * 32;
   decode_prepare_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
-      (const __half*)basis_f16, (const __half*)coeff_scale, (const __half*)mean_f16, nkv, rank, (uint2*)wprep_out);
+      (const __half*)basis_f16, (const __half*)coeff_scale, (const __half*)mean_f16, nkv, rank,
+      (uint2*)((unsigned char*)wprep_out + tc_wprep_bytes(nkv, rank)));
   SHARD_CHECK_LAUNCH();
   return SHARD_OK;
 }
@@ -614,10 +495,11 @@ static int check_shape(const ShardDecodeShape* sh) {
   return SHARD_OK;
 }
 
-// scratch layout: [batch][n_parts][n_q][132] fp32 partial records, then (batch > 1) `batch` out pointers
+// scratch layout: 16-byte header (status word), [batch][n_parts][n_q][132] fp32 partial records,
+// then (batch > 1) `batch` out pointers
 static size_t ws_bytes(const ShardDecodeShape& sh, int batch) {
   const DecodePlan pl = make_plan(sh, batch);
-  size_t b = (size_t)batch * pl.n_parts * sh.n_q * PART * sizeof(float);
+  size_t b = WS_HEADER_BYTES + (size_t)batch * pl.n_parts * sh.n_q * PART * sizeof(float);
   if (batch > 1) b += (size_t)batch * sizeof(void*);
   return b;
 }
@@ -665,7 +547,8 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
   p.sh = sh;
   p.inv_freq = inv_freq;
   p.codebook = codebook;
-  p.ws = (float*)workspace;
+  p.ws = (float*)((unsigned char*)workspace + WS_HEADER_BYTES);
+  p.status = (int*)workspace;
   p.n_chunks = pl.n_chunks;
   p.tiles_per_chunk = pl.tiles_per_chunk;
   p.n_fp16_ctas = pl.n_fp16_ctas;
@@ -673,20 +556,24 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
   p.n_parts = pl.n_parts;
 
   dim3 grid(pl.n_parts, sh.nkv, batch);
-  switch (sh.rank / 32) {
-    case 1: rc = launch_partial<1>(p, grid, st); break;
-    case 2: rc = launch_partial<2>(p, grid, st); break;
-    case 3: rc = launch_partial<3>(p, grid, st); break;
-    case 4: rc = launch_partial<4>(p, grid, st); break;
-    case 5: rc = launch_partial<5>(p, grid, st); break;
-    default: rc = launch_partial<6>(p, grid, st); break;
+  if (use_tc()) {
+    rc = launch_partial_tc(p, grid, st);
+  } else {
+    switch (sh.rank / 32) {
+      case 1: rc = launch_partial<1>(p, grid, st); break;
+      case 2: rc = launch_partial<2>(p, grid, st); break;
+      case 3: rc = launch_partial<3>(p, grid, st); break;
+      case 4: rc = launch_partial<4>(p, grid, st); break;
+      case 5: rc = launch_partial<5>(p, grid, st); break;
+      default: rc = launch_partial<6>(p, grid, st); break;
+    }
   }
   if (rc) return rc;
   SHARD_CHECK_LAUNCH();
 
   void** out_table = nullptr;
   if (batch > 1) {
-    out_table = reinterpret_cast<void**>(reinterpret_cast<unsigned char*>(workspace) +
+    out_table = reinterpret_cast<void**>(reinterpret_cast<unsigned char*>(workspace) + WS_HEADER_BYTES +
                                          (size_t)batch * pl.n_parts * sh.n_q * PART * sizeof(float));
     gather_out_ptrs_kernel<<<(batch + 127) / 128, 128, 0, st>>>(seqs, batch, out_table);
   }
