@@ -33,6 +33,7 @@ extern "C" {
 #define SHARD_E_ARG (-1)       /* null pointer, bad size or unsupported geometry  */
 #define SHARD_E_WORKSPACE (-2) /* workspace too small                             */
 #define SHARD_E_ALIGN (-3)     /* pointer not aligned as documented               */
+#define SHARD_E_TOO_LARGE (-4) /* more scratch needed than the built-in area holds */
 
 #define SHARD_HEAD_DIM 128
 #define SHARD_PART_STRIDE 132  /* floats per (part, head) record: m, l, 0, 0, acc[128] */
@@ -137,6 +138,38 @@ size_t shard_b200_decode_workspace_bytes(const ShardDecodeShape* shape_host, int
 int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const ShardDecodeShape* shape_host,
                            const float* inv_freq, const float* codebook, void* workspace,
                            size_t workspace_bytes, void* stream);
+
+/*
+ * Size of the scratch area that lives inside the library's device image and is used by
+ * shard_b200_decode_attn_noalloc.  Every GPU that loads the library sets this much memory
+ * aside until the process exits.
+ */
+#define SHARD_B200_STATIC_SCRATCH_BYTES (2u << 20)
+
+/*
+ * shard_b200_decode_attn for one sequence, for callers that cannot allocate device memory
+ * and so have no workspace to pass: for example a server that freezes its device-memory
+ * plan at start-up and forbids cudaMalloc afterwards, or a host program that only lends
+ * this library its tensors and offers no allocator.  The scratch comes from a fixed
+ * 2 MiB area built into the library; inputs and outputs are still the caller's
+ * (`seq_host` is a host pointer to one ShardSeq, exactly as with batch == 1 above).
+ * This entry point has no counterpart in the reference.
+ *
+ *   - Shapes whose split-KV records do not fit in SHARD_B200_STATIC_SCRATCH_BYTES are
+ *     refused with SHARD_E_TOO_LARGE and nothing is launched.  With 32 query heads the
+ *     area holds 124 records per head: a middle segment of any length (at most 37 chunks)
+ *     plus the sink/window record plus about 2,700 streamed tokens.
+ *   - No cudaMalloc / cudaFree or other allocating call is made, now or later.
+ *   - The first call on a device looks up the device address of the built-in area
+ *     (cudaGetSymbolAddress, with that device current) and remembers it; make that
+ *     first call before starting any stream capture.
+ *   - All calls on a device share the one area, and it keeps the previous call's
+ *     contents (the part that must start at zero is cleared on `stream` by each call).
+ *     Two calls whose kernels can overlap on the GPU -- different streams without an
+ *     ordering between them -- race on it and give wrong results; serialise them.
+ */
+int shard_b200_decode_attn_noalloc(const ShardSeq* seq_host, const ShardDecodeShape* shape_host,
+                                   const float* inv_freq, const float* codebook, void* stream);
 
 /*
  * Log-sum-exp combine of `n_parts` partials (fp32 [n_parts][n_q][132]) into fp16

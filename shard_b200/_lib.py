@@ -42,6 +42,8 @@ _SIGNATURES = {
     "shard_b200_decode_workspace_bytes": (C.c_size_t, [C.POINTER(ShardDecodeShape), C.c_int32]),
     "shard_b200_decode_attn": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(ShardDecodeShape), C.c_void_p,
                                          C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "shard_b200_decode_attn_noalloc": (C.c_int, [C.c_void_p, C.POINTER(ShardDecodeShape), C.c_void_p, C.c_void_p,
+                                                 C.c_void_p]),
     "shard_b200_lse_merge": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "shard_b200_stream_quantize": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                              C.c_void_p]),

@@ -19,6 +19,7 @@
 // the packed int4 coefficients (nibbles are expanded to fp16 in registers), rotates
 // them by the relative phase, and dots them with the un-rotated query.
 #include <cstdlib>
+#include <mutex>
 
 #include "decode_common.cuh"
 
@@ -590,6 +591,61 @@ extern "C" int shard_b200_lse_merge(const float* parts, int32_t n_parts, int32_t
   return SHARD_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Decode entry point for callers that cannot allocate device memory
+// ---------------------------------------------------------------------------
+// The split-KV pass needs a few hundred KB of scratch for its per-chunk partial records.
+// The regular entry point takes that scratch from the caller.  Some callers have no way
+// to provide it: an inference server that fixes its whole device-memory plan at start-up
+// and forbids any later cudaMalloc (so a request can never fail or fragment memory half
+// way through), or a host application that only hands this library its tensors and
+// exposes no allocator at all.  For them the library carries one fixed scratch area
+// inside its own device image.  It costs SHARD_B200_STATIC_SCRATCH_BYTES on every GPU
+// that loads the library, for as long as the process lives.
+static __device__ __align__(256) unsigned char g_static_scratch[SHARD_B200_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};   // device address of the array, per device
+std::mutex g_static_scratch_mutex;
+
+// `g_static_scratch` names a host-side handle here, not device memory: the address a kernel
+// can use has to be asked from the runtime, once per device, with that device current.
+int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return SHARD_E_ARG;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (!g_static_scratch_addr[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return SHARD_OK;
+}
+}  // namespace
+
+extern "C" int shard_b200_decode_attn_noalloc(const ShardSeq* seq_host, const ShardDecodeShape* shape_host,
+                                              const float* inv_freq, const float* codebook, void* stream) {
+  if (!seq_host || !inv_freq) return SHARD_E_ARG;
+  int rc = check_shape(shape_host);
+  if (rc != SHARD_OK) return rc;
+  const size_t need = ws_bytes(*shape_host, 1);
+  if (need > (size_t)SHARD_B200_STATIC_SCRATCH_BYTES) return SHARD_E_TOO_LARGE;
+  void* scratch = nullptr;
+  rc = static_scratch_for_current_device(&scratch);
+  if (rc != SHARD_OK) return rc;
+  // The array still holds whatever the previous call left there.  Only the status word in
+  // the header has to start at zero; every partial record is rewritten before it is read.
+  cudaError_t e = cudaMemsetAsync(scratch, 0, WS_HEADER_BYTES, (cudaStream_t)stream);
+  if (e != cudaSuccess) return (int)e;
+  return shard_b200_decode_attn(seq_host, 1, shape_host, inv_freq, codebook, scratch,
+                                (size_t)SHARD_B200_STATIC_SCRATCH_BYTES, stream);
+}
+
 extern "C" int shard_b200_abi_version(void) { return 1; }
 
 extern "C" const char* shard_b200_status_string(int status) {
@@ -598,6 +654,7 @@ extern "C" const char* shard_b200_status_string(int status) {
     case SHARD_E_ARG: return "invalid argument (null pointer, bad size or unsupported geometry)";
     case SHARD_E_WORKSPACE: return "workspace too small";
     case SHARD_E_ALIGN: return "pointer not aligned as documented";
+    case SHARD_E_TOO_LARGE: return "request needs more scratch than the library's built-in 2 MiB area";
     default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown status";
   }
 }
