@@ -31,6 +31,7 @@ constexpr int TILE_TOK = 16;           // tokens per warp tile of the mma.sync k
 constexpr int MMA_CTA_SLOTS = 148 * 3; // resident CTAs of the mma.sync kernel on a B200
 constexpr int TC_TILE_TOK = 128;       // tokens per CTA tile of the tcgen05 kernel
 constexpr int TC_CTA_SLOTS = 148 * 2;  // two resident CTAs per SM
+constexpr int PIPE_CTA_SLOTS = 148;    // the pipelined kernel keeps one CTA per SM
 constexpr int WS_HEADER_BYTES = 16;    // status word + padding in front of the partial records
 
 // implemented in decode_tc.cu
@@ -38,35 +39,47 @@ size_t tc_wprep_bytes(int nkv, int rank);
 int launch_prepare_tc(const void* basis, const void* cscale, const void* mean, int nkv, int rank, void* out,
                       cudaStream_t st);
 int launch_partial_tc(const DecodeParams& p, dim3 grid, cudaStream_t st);
+// implemented in decode_pipe.cu
+int launch_partial_pipe(const DecodeParams& p, dim3 grid, cudaStream_t st);
 
 __host__ __device__ inline size_t tc_blob_bytes(int nkv, int rank) {
   return (size_t)nkv * (((rank + 63) / 64) * 16384 + 512);
 }
 
 struct DecodePlan {
-  int n_chunks, tiles_per_chunk, n_fp16_ctas, n_stream_ctas, n_parts;
+  int n_chunks, tiles_per_chunk, tiles_rem, n_fp16_ctas, n_stream_ctas, n_parts;
 };
 
-// Which kernel walks the compressed middle: the tcgen05 kernel (default) or the older
-// mma.sync kernel, kept for A/B timing (environment SHARD_B200_DECODE=mma).
-static bool use_tc() {
+// Which kernel walks the compressed middle: the pipelined tcgen05 kernel (default), or one of
+// the two earlier kernels kept for A/B timing (environment SHARD_B200_DECODE=tc1 | mma).
+enum DecodeMode { MODE_PIPE = 0, MODE_TC1 = 1, MODE_MMA = 2 };
+static DecodeMode decode_mode() {
   static int mode = -1;
   if (mode < 0) {
     const char* e = getenv("SHARD_B200_DECODE");
-    mode = (e && e[0] == 'm') ? 0 : 1;
+    mode = (e && e[0] == 'm') ? MODE_MMA : (e && e[0] == 't') ? MODE_TC1 : MODE_PIPE;
   }
-  return mode == 1;
+  return (DecodeMode)mode;
 }
 
 static DecodePlan make_plan(const ShardDecodeShape& sh, int batch) {
   DecodePlan pl{};
-  const bool tc = use_tc();
-  const int tile_tok = tc ? TC_TILE_TOK : TILE_TOK;
-  const int slots = tc ? TC_CTA_SLOTS : MMA_CTA_SLOTS;
+  const DecodeMode mode = decode_mode();
+  const int tile_tok = (mode == MODE_MMA) ? TILE_TOK : TC_TILE_TOK;
   const int n_tok = sh.tok_end - sh.tok_begin;
   const int n_tiles = (n_tok + tile_tok - 1) / tile_tok;
-  if (n_tiles > 0) {
-    const int groups = sh.nkv * batch;
+  const int groups = sh.nkv * batch;
+  if (n_tiles > 0 && mode == MODE_PIPE) {
+    // one CTA per SM: spread the tiles of every (sequence, KV head) evenly over its CTAs
+    int chunks = (groups >= PIPE_CTA_SLOTS) ? (n_tiles + 15) / 16 : PIPE_CTA_SLOTS / groups;
+    if (chunks > n_tiles) chunks = n_tiles;
+    if (chunks < 1) chunks = 1;
+    pl.n_chunks = chunks;
+    pl.tiles_per_chunk = n_tiles / chunks;
+    pl.tiles_rem = n_tiles % chunks;
+  } else if (n_tiles > 0) {
+    const bool tc = mode == MODE_TC1;
+    const int slots = tc ? TC_CTA_SLOTS : MMA_CTA_SLOTS;
     int tpc;
     if (groups >= slots / 2) {
       tpc = tc ? 8 : 64;
@@ -552,12 +565,16 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
   p.status = (int*)workspace;
   p.n_chunks = pl.n_chunks;
   p.tiles_per_chunk = pl.tiles_per_chunk;
+  p.tiles_rem = pl.tiles_rem;
   p.n_fp16_ctas = pl.n_fp16_ctas;
   p.n_stream_ctas = pl.n_stream_ctas;
   p.n_parts = pl.n_parts;
 
   dim3 grid(pl.n_parts, sh.nkv, batch);
-  if (use_tc()) {
+  if (decode_mode() == MODE_PIPE) {
+    if (batch == 1 && ((uintptr_t)p.one.k_coeffs & 15)) return SHARD_E_ALIGN;
+    rc = launch_partial_pipe(p, grid, st);
+  } else if (decode_mode() == MODE_TC1) {
     rc = launch_partial_tc(p, grid, st);
   } else {
     switch (sh.rank / 32) {

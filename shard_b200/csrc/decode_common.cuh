@@ -19,6 +19,7 @@ struct DecodeParams {
   int* status;          // device word set non-zero when a bounded wait gave up
   int n_chunks;         // CTAs (per KV head) that walk the compressed middle
   int tiles_per_chunk;
+  int tiles_rem;        // pipelined kernel: the first tiles_rem chunks walk one tile more
   int n_fp16_ctas;      // 1 if there are sink / window rows
   int n_stream_ctas;
   int n_parts;          // n_chunks + n_fp16_ctas + n_stream_ctas

@@ -1,0 +1,516 @@
+// Split-KV decode pass, warp-specialised and pipelined three tiles deep (tcgen05 + TMEM).
+//
+// One CTA per SM (16 warps) owns one KV head and a run of 128-token tiles of the compressed
+// middle segment.  Three tiles are in flight at any time, each in its own 128-column
+// tensor-memory stage:
+//
+//   unpack warps (4)    packed int4 coefficients -> fp16 A operand in tensor memory (one A slot,
+//                       recycled as soon as MMA1 of the previous tile has read it); one elected
+//                       thread then issues
+//                       MMA1  K_n[128 tok x 128] = A . W^T           (A from TMEM, W in smem)
+//   consumer groups (3 x 4 warps; group g owns stage g and tiles g, g+3, ...)
+//                       thread = token row: K_n -> + mean -> half2 -> rotate by the relative
+//                       phase -> K~ written in place; expand the token's 32 VQ codes into the
+//                       stage's V tile; one elected thread of the group issues
+//                       MMA2  S[128 tok x 16]    = K~ . Q^T          (A = K~ from TMEM)
+//                       per-warp online softmax -> P; the elected thread issues
+//                       MMA3  O[128 ch x 16]     = V^T . P^T         (V, P in smem)
+//                       and every thread rescales-and-accumulates its output channel
+//
+// Stage s of tensor memory: columns [128s, 128s+128): un-rotated keys (fp32), overwritten in
+// place by K~ (fp16x2, columns 0-63 of the stage), scores (64-79) and the tile's P.V (80-95).
+// Every hand-over is an mbarrier; every wait is bounded and raises the CTA's abort flag when it
+// gives up, after which all roles drain, tensor memory is freed and the status word is set.
+#include "decode_common.cuh"
+#include "tcgen05.cuh"
+
+namespace shard {
+
+constexpr int PP_STAGES = 3;
+constexpr int PP_CONS_WARPS = 12;
+constexpr int PP_UNPACK_WARP0 = 12;
+constexpr int PP_WARPS = 16;
+constexpr int PP_THREADS = PP_WARPS * 32;
+constexpr int PP_TMEM_COLS = 512;
+constexpr int PP_COL_A = 384;         // A operand slot, R/2 columns
+constexpr int PP_COL_S = 64;          // within a stage
+constexpr int PP_COL_O = 80;
+constexpr int PP_V_BYTES = 32768, PP_P_BYTES = 4096, PP_Q_BYTES = 4096, PP_CB_BYTES = 2048, PP_MEAN_BYTES = 512;
+#ifdef SHARD_TC_DEBUG
+constexpr int PP_MISC_BYTES = 1024 + 1024 + 512;   // + per-role timing accumulators
+#else
+constexpr int PP_MISC_BYTES = 1024 + 1024;   // state + barriers, and slack for 1 KB alignment
+#endif
+
+__host__ __device__ constexpr int pp_w_bytes(int nw) { return ((nw + 1) / 2) * 16384; }
+__host__ __device__ constexpr int pp_smem_bytes(int nw) {
+  return pp_w_bytes(nw) + PP_STAGES * (PP_V_BYTES + PP_P_BYTES) + PP_Q_BYTES + PP_CB_BYTES + PP_MEAN_BYTES + PP_MISC_BYTES;
+}
+
+// single-thread forms (the caller is one elected thread)
+__device__ __forceinline__ void umma_ss_1t(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_ts_1t(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit_1t(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Barrier among a subset of the CTA's warps (id 1..15, `count` threads) that also ORs a flag
+// over the participants.  The roles use it to agree on giving up: a warp whose bounded wait
+// failed never leaves its siblings alone at a barrier -- everybody reaches the barrier, learns
+// the combined flag and leaves the tile loop together.
+__device__ __forceinline__ bool named_bar_or(int id, int count, bool flag) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %3, 0;\n\t"
+      "bar.red.or.pred p, %1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out) : "r"(id), "r"(count), "r"((uint32_t)flag) : "memory");
+  return out != 0;
+}
+
+#ifdef SHARD_TC_DEBUG
+// development aid: per-CTA, per-role phase accounting (role 0: consumer warp 0, 1: unpack warp 12,
+// 2: MMA thread); slot k accumulates the cycles that ended at stamp k
+__device__ long long* g_pp_debug = nullptr;
+#define PP_T0(role) long long pp_last__ = clock64(); \
+  long long* pp_rec__ = g_pp_debug ? reinterpret_cast<long long*>(smem + pp_smem_bytes(NW) - 1024 - 512) + 16 * (role) : nullptr
+#define PP_T(slot) do { if (pp_rec__ && lane == 0) { const long long n__ = clock64(); pp_rec__[(slot)] += n__ - pp_last__; pp_last__ = clock64(); } } while (0)
+extern "C" int shard_b200_pp_debug_set(long long* buf) { return (int)cudaMemcpyToSymbol(g_pp_debug, &buf, sizeof(buf)); }
+#else
+#define PP_T0(role) do {} while (0)
+#define PP_T(slot) do {} while (0)
+#endif
+
+template <int NW>  // rank / 32
+__global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(const __grid_constant__ DecodeParams p) {
+  constexpr int R = NW * 32;
+  constexpr int KC = R / 8;          // 32-bit words of nibbles per coefficient row
+  constexpr int KSTEPS = R / 16;
+  constexpr int W_BYTES = pp_w_bytes(NW);
+
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* w_s = smem;
+  unsigned char* v_s = w_s + W_BYTES;                              // [3] V tiles, MN-major, 128B swizzle
+  unsigned char* p_s = v_s + PP_STAGES * PP_V_BYTES;               // [3] P operands [16 x 128 tok]
+  unsigned char* q_s = p_s + PP_STAGES * PP_P_BYTES;               // Q operand [16 x 128]
+  uint2* cbv = reinterpret_cast<uint2*>(q_s + PP_Q_BYTES);         // V codebook
+  float* mean_s = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(cbv) + PP_CB_BYTES);
+  float* misc = mean_s + 128;
+  float* alpha_s = misc;                                           // [3][16]
+  float* m_s = misc + 48;                                          // [3][16]
+  float* l_s = misc + 96;                                          // [3][16]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 144);
+  volatile int* abort_s = reinterpret_cast<volatile int*>(misc + 145);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(misc + 148);        // 20 mbarriers
+
+  const ShardSeq& sq = p.table ? p.table[blockIdx.z] : p.one;
+  const ShardDecodeShape& sh = p.sh;
+  const int kv = blockIdx.y;
+  const int part = blockIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  float* rec_base = p.ws + (((size_t)blockIdx.z * p.n_parts + part) * sh.n_q + (size_t)kv * GQA) * PART;
+
+#ifdef SHARD_TC_DEBUG
+  const long long pp_kstart__ = clock64();
+#endif
+  if (part >= p.n_chunks) {
+    // sink + window rows, or streamed rows: warp-per-token path
+    float* qn = reinterpret_cast<float*>(smem);
+    float* qr = qn + GQA * HD;
+    float* cbs = qr + GQA * HD;
+    float* scratch = cbs + 256;
+    const bool is_fp16 = part < p.n_chunks + p.n_fp16_ctas;
+    if (!is_fp16) for (int i = tid; i < 256; i += PP_THREADS) cbs[i] = p.codebook[i];
+    if (tid < HD) stage_query(sq, kv, sh.pos_q, p.inv_freq, tid, qn, qr);
+    __syncthreads();
+    int u_lo = 0, u_hi = sh.n_sink + sh.n_win;
+    if (!is_fp16) {
+      u_lo = (part - p.n_chunks - p.n_fp16_ctas) * STREAM_TOK_PER_CTA;
+      u_hi = min(u_lo + STREAM_TOK_PER_CTA, sh.n_stream);
+    }
+    SoftmaxState st;
+    softmax_init(st);
+    process_rows<PP_WARPS>(st, sq, sh, kv, is_fp16, u_lo, u_hi, qr, cbs, warp, lane);
+    __syncthreads();
+    emit_partial<PP_WARPS>(st, scratch, rec_base, tid, warp, lane);
+    return;
+  }
+
+  // barrier addresses
+  const uint32_t bar0 = smem_u32(bars);
+  auto KN_FULL = [&](int s) { return bar0 + 8u * (uint32_t)s; };          // MMA1 of the stage's tile done
+  auto S_FULL = [&](int s) { return bar0 + 8u * (uint32_t)(3 + s); };     // MMA2 done
+  auto O_FULL = [&](int s) { return bar0 + 8u * (uint32_t)(6 + s); };     // MMA3 done
+  auto T_EMPTY = [&](int s) { return bar0 + 8u * (uint32_t)(9 + s); };    // consumers have drained the stage
+  const uint32_t A_EMPTY = bar0 + 8u * 12u;                               // MMA1 has read the A slot
+
+  // ---- one-time setup -------------------------------------------------------------------
+  {
+    const unsigned char* blob = reinterpret_cast<const unsigned char*>(sq.k_wprep) + (size_t)kv * (W_BYTES + PP_MEAN_BYTES);
+    const uint4* src = reinterpret_cast<const uint4*>(blob);
+    uint4* dst = reinterpret_cast<uint4*>(w_s);
+    for (int i = tid; i < W_BYTES / 16; i += PP_THREADS) dst[i] = src[i];
+    if (tid < 128) mean_s[tid] = reinterpret_cast<const float*>(blob + W_BYTES)[tid];
+    if (tid < 256) cbv[tid] = reinterpret_cast<const uint2*>(sq.v_centroids)[tid];
+    uint4* z = reinterpret_cast<uint4*>(p_s);
+    for (int i = tid; i < (PP_STAGES * PP_P_BYTES + PP_Q_BYTES) / 16; i += PP_THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
+#ifdef SHARD_TC_DEBUG
+    if (tid < 48) reinterpret_cast<long long*>(smem + pp_smem_bytes(NW) - 1024 - 512)[tid] = 0;
+#endif
+    if (tid == 0) {
+      for (int s = 0; s < PP_STAGES; ++s) {
+        mbar_init(KN_FULL(s), 1); mbar_init(S_FULL(s), 1); mbar_init(O_FULL(s), 1); mbar_init(T_EMPTY(s), 4);
+      }
+      mbar_init(A_EMPTY, 1);
+      *abort_s = 0;
+    }
+  }
+  __syncthreads();
+  if (tid < HD) {
+    // un-rotated query (fp16 arithmetic as the reference) -> Q operand rows 0..3; element of pair i
+    // (c or d part) sits at the contraction position of the in-place K~ layout: column
+    // 8*(i/8) + (i%8)/2 (+4 for the d part), two elements per column
+    const int d = tid, i = d & 63;
+    const int kk = 2 * (8 * (i >> 3) + ((i & 7) >> 1) + (d >= 64 ? 4 : 0)) + (i & 1);
+    const float phase = __fmul_rn((float)sh.pos_q, p.inv_freq[i]);
+    float sn, cs;
+    sincosf(phase, &sn, &cs);
+    const __half c16 = __float2half_rn(cs), s16 = __float2half_rn(sn);
+    const __half* qg = reinterpret_cast<const __half*>(sq.q) + (size_t)kv * GQA * HD;
+#pragma unroll
+    for (int h = 0; h < GQA; ++h) {
+      const __half x = qg[h * HD + d];
+      const __half other = qg[h * HD + (d ^ 64)];
+      const __half rot = (d < 64) ? __hneg(other) : other;
+      const __half un = __hsub(__hmul(x, c16), __hmul(rot, s16));
+      *reinterpret_cast<__half*>(q_s + (kk >> 6) * 2048 + sw128_off(h, (kk >> 3) & 7) + (kk & 7) * 2) = un;
+    }
+  }
+  if (warp == PP_UNPACK_WARP0) {
+    tmem_alloc(smem_u32(tmem_slot), PP_TMEM_COLS);
+    tmem_relinquish();
+  }
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+#ifdef SHARD_TC_DEBUG
+  if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 48] += clock64() - pp_kstart__;
+#endif
+
+  // tiles of this chunk: evenly spread, the first `tiles_rem` chunks get one more
+  const int tile_lo = part * p.tiles_per_chunk + min(part, p.tiles_rem);
+  const int n_my = p.tiles_per_chunk + (part < p.tiles_rem ? 1 : 0);
+
+  float acc[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+  float run_m[GQA], run_l[GQA];
+#pragma unroll
+  for (int h = 0; h < GQA; ++h) { run_m[h] = neg_inf(); run_l[h] = 0.f; }
+
+  if (warp < PP_CONS_WARPS) {
+    // =============================== consumer groups ======================================
+    const int g = warp >> 2, quad = warp & 3, m = quad * 32 + lane;
+    const uint32_t T_g = tmem_base + (uint32_t)(128 * g);
+    const uint32_t lane_T = T_g + ((uint32_t)(quad * 32) << 16);
+    constexpr uint32_t IDESC2 = umma_idesc(128, 16, false, false);
+    constexpr uint32_t IDESC3 = umma_idesc(128, 16, true, false);
+    const uint64_t qdesc = smem_desc_sw128(smem_u32(q_s), 16, 1024);
+    const uint64_t vdesc = smem_desc_sw128(smem_u32(v_s + g * PP_V_BYTES), 16384, 1024);
+    const uint64_t pdesc = smem_desc_sw128(smem_u32(p_s + g * PP_P_BYTES), 16, 1024);
+    unsigned char* v_g = v_s + g * PP_V_BYTES;
+    unsigned char* p_g = p_s + g * PP_P_BYTES;
+    float* alpha_g = alpha_s + 16 * g;
+    const uint32_t* phase_tab = reinterpret_cast<const uint32_t*>(sq.phase);
+    const uint8_t* vidx = sq.v_indices + (size_t)kv * sh.n_comp * VQ_GROUPS;
+    PP_T0(0);
+#ifdef SHARD_TC_DEBUG
+    if (warp != 0) pp_rec__ = nullptr;
+#endif
+
+    bool bad = false;
+    for (int it = g; it < n_my; it += PP_STAGES) {
+      const uint32_t par = (uint32_t)((it / PP_STAGES) & 1);
+      const int t0 = sh.tok_begin + (tile_lo + it) * 128;
+      const int tok = min(t0 + m, sh.tok_end - 1);
+      const bool valid = (t0 + m) < sh.tok_end;
+      const uint4* prow = reinterpret_cast<const uint4*>(phase_tab + (size_t)(tok - sh.tok_begin) * 64);
+      uint4 pc = prow[0], ps = prow[8];          // cos words 0-31 (uint4 0-7), sin words 32-63 (uint4 8-15)
+
+      PP_T(0);
+      bad |= !mbar_wait(KN_FULL(g), par, abort_s);
+      tc_fence_after();
+      PP_T(1);
+      const uint4 codes0 = *reinterpret_cast<const uint4*>(vidx + (size_t)tok * VQ_GROUPS);
+      const uint4 codes1 = *reinterpret_cast<const uint4*>(vidx + (size_t)tok * VQ_GROUPS + 16);
+
+      // ---- rotate: 8 chunks of 8 pairs; K~ goes back in place --------------------------------
+      // chunk ch reads c columns [8ch, 8ch+8) and d columns [64+8ch, ...) and writes 4 columns of c'
+      // and 4 of d' (two pairs per column) over the 8 c columns it has just consumed
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint32_t cr[8], dr[8];
+        tmem_ld_x8(lane_T + 8 * ch, cr);
+        tmem_ld_x8(lane_T + 64 + 8 * ch, dr);
+        const uint32_t cos2[4] = {pc.x, pc.y, pc.z, pc.w};
+        const uint32_t sin2[4] = {ps.x, ps.y, ps.z, ps.w};
+        if (ch < 7) { pc = prow[ch + 1]; ps = prow[8 + ch + 1]; }
+        PP_T(13);
+        tmem_wait_ld();
+        PP_T(14);
+        uint32_t oc[4], od[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 mc = *reinterpret_cast<const float2*>(mean_s + 8 * ch + 2 * j);
+          const float2 md = *reinterpret_cast<const float2*>(mean_s + 64 + 8 * ch + 2 * j);
+          const __half2 c2 = __floats2half2_rn(__uint_as_float(cr[2 * j]) + mc.x, __uint_as_float(cr[2 * j + 1]) + mc.y);
+          const __half2 d2 = __floats2half2_rn(__uint_as_float(dr[2 * j]) + md.x, __uint_as_float(dr[2 * j + 1]) + md.y);
+          const __half2 cs = as_half2(cos2[j]), sn = as_half2(sin2[j]);
+          oc[j] = as_u32(__hfma2(c2, cs, __hneg2(__hmul2(d2, sn))));   // c cos - d sin
+          od[j] = as_u32(__hfma2(d2, cs, __hmul2(c2, sn)));            // d cos + c sin
+        }
+        tmem_st_x4(lane_T + 8 * ch, oc);
+        tmem_st_x4(lane_T + 8 * ch + 4, od);
+      }
+      PP_T(2);
+      // ---- gather the token's V row (32 codes) into the stage's V tile -------------------------
+      {
+        const uint32_t cw[8] = {codes0.x, codes0.y, codes0.z, codes0.w, codes1.x, codes1.y, codes1.z, codes1.w};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const uint32_t two = cw[j >> 1] >> (16 * (j & 1));
+          const uint2 e0 = cbv[two & 0xff], e1 = cbv[(two >> 8) & 0xff];
+          *reinterpret_cast<uint4*>(v_g + (j >> 3) * 16384 + sw128_off(m, j & 7)) = make_uint4(e0.x, e0.y, e1.x, e1.y);
+        }
+      }
+      PP_T(8);
+      tmem_wait_st();
+      PP_T(9);
+      fence_proxy_async();
+      PP_T(10);
+      tc_fence_before();
+      bad = named_bar_or(1 + g, 128, bad || *abort_s);
+      if (bad) break;                                   // uniform over the group
+      if (quad == 0 && lane == 0) {
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts_1t(T_g + PP_COL_S, T_g + 8 * ks, qdesc + (uint64_t)(((ks >> 2) * 2048 + (ks & 3) * 32) >> 4), IDESC2,
+                     ks > 0 ? 1u : 0u);
+        umma_commit_1t(S_FULL(g));
+      }
+      __syncwarp();
+      PP_T(3);
+
+      // ---- softmax over this warp's 32 tokens ---------------------------------------------------
+      bad |= !mbar_wait(S_FULL(g), par, abort_s);
+      tc_fence_after();
+      PP_T(4);
+      {
+        uint32_t sraw[4];
+        tmem_ld_x4(lane_T + PP_COL_S, sraw);
+        tmem_wait_ld();
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) {
+          const float s = valid ? __uint_as_float(sraw[h]) * INV_SQRT_HD : neg_inf();
+          const float tm = warp_max(s);
+          const float mn = fmaxf(run_m[h], tm);
+          const float al = (run_m[h] == neg_inf()) ? 0.f : exp2f((run_m[h] - mn) * LOG2E);
+          const float pr = valid ? exp2f((s - mn) * LOG2E) : 0.f;
+          run_m[h] = mn;
+          run_l[h] = run_l[h] * al + pr;
+          const int n = 4 * quad + h;
+          *reinterpret_cast<__half*>(p_g + (m >> 6) * 2048 + sw128_off(n, (m >> 3) & 7) + (m & 7) * 2) = __float2half_rn(pr);
+          if (lane == 0) alpha_g[n] = al;
+        }
+      }
+      PP_T(11);
+      fence_proxy_async();
+      PP_T(12);
+      tc_fence_before();
+      bad = named_bar_or(1 + g, 128, bad || *abort_s);
+      if (bad) break;                                   // uniform over the group
+      if (quad == 0 && lane == 0) {
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ss_1t(T_g + PP_COL_O, vdesc + (uint64_t)((ks * 2048) >> 4),
+                     pdesc + (uint64_t)(((ks >> 2) * 2048 + (ks & 3) * 32) >> 4), IDESC3, ks > 0 ? 1u : 0u);
+        umma_commit_1t(O_FULL(g));
+      }
+      __syncwarp();
+      PP_T(5);
+
+      // ---- accumulate channel m of the tile's P.V ------------------------------------------------
+      bad |= !mbar_wait(O_FULL(g), par, abort_s);
+      tc_fence_after();
+      PP_T(6);
+      {
+        uint32_t o[16];
+        tmem_ld_x16(lane_T + PP_COL_O, o);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+          const float4 al = *reinterpret_cast<const float4*>(alpha_g + 4 * j4);
+          acc[4 * j4 + 0] = fmaf(acc[4 * j4 + 0], al.x, __uint_as_float(o[4 * j4 + 0]));
+          acc[4 * j4 + 1] = fmaf(acc[4 * j4 + 1], al.y, __uint_as_float(o[4 * j4 + 1]));
+          acc[4 * j4 + 2] = fmaf(acc[4 * j4 + 2], al.z, __uint_as_float(o[4 * j4 + 2]));
+          acc[4 * j4 + 3] = fmaf(acc[4 * j4 + 3], al.w, __uint_as_float(o[4 * j4 + 3]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(T_EMPTY(g));
+      PP_T(7);
+    }
+  } else {
+    // =============================== unpack warps (+ MMA1 issue) =========================
+    constexpr uint32_t IDESC1 = umma_idesc(128, 128, false, false);
+    const uint64_t wdesc = smem_desc_sw128(smem_u32(w_s), 16, 1024);
+    const int quad = warp - PP_UNPACK_WARP0, m = quad * 32 + lane;
+    const uint32_t lane_A = tmem_base + PP_COL_A + ((uint32_t)(quad * 32) << 16);
+    uint4 x[NW];
+    {
+      const int tok = min(sh.tok_begin + tile_lo * 128 + m, sh.tok_end - 1);
+      const uint4* row = reinterpret_cast<const uint4*>(sq.k_coeffs + (size_t)tok * (R / 2));
+#pragma unroll
+      for (int i = 0; i < NW; ++i) x[i] = row[i];
+    }
+    PP_T0(1);
+#ifdef SHARD_TC_DEBUG
+    if (warp != PP_UNPACK_WARP0) pp_rec__ = nullptr;
+#endif
+    bool bad = false;
+    for (int it = 0; it < n_my; ++it) {
+      if (it > 0) {
+        bad |= !mbar_wait(A_EMPTY, (uint32_t)((it - 1) & 1), abort_s);
+        tc_fence_after();
+      }
+      PP_T(0);
+#pragma unroll
+      for (int i = 0; i < NW; ++i) {
+        const uint32_t wv[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
+        uint32_t o[16];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          o[4 * e + 0] = nib2half2_tc(wv[e]);          // ranks 8c+0, 8c+4 of word c = 4i+e
+          o[4 * e + 1] = nib2half2_tc(wv[e] >> 4);     //       8c+1, 8c+5
+          o[4 * e + 2] = nib2half2_tc(wv[e] >> 8);     //       8c+2, 8c+6
+          o[4 * e + 3] = nib2half2_tc(wv[e] >> 12);    //       8c+3, 8c+7
+        }
+        tmem_st_x16(lane_A + 16 * i, o);
+      }
+      if (it + 1 < n_my) {
+        const int tok = min(sh.tok_begin + (tile_lo + it + 1) * 128 + m, sh.tok_end - 1);
+        const uint4* row = reinterpret_cast<const uint4*>(sq.k_coeffs + (size_t)tok * (R / 2));
+#pragma unroll
+        for (int i = 0; i < NW; ++i) x[i] = row[i];
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      bad = named_bar_or(4, 128, bad || *abort_s);
+      if (bad) break;                                   // uniform over the four unpack warps
+      PP_T(1);
+      if (quad == 0) {
+        if (lane == 0) {
+          const int s = it % PP_STAGES, use = it / PP_STAGES;
+          if (use > 0) mbar_wait(T_EMPTY(s), (uint32_t)((use - 1) & 1), abort_s);
+          tc_fence_after();
+          const uint32_t T = tmem_base + 128u * (uint32_t)s;
+#pragma unroll
+          for (int ks = 0; ks < KSTEPS; ++ks)
+            umma_ts_1t(T, tmem_base + PP_COL_A + 8 * ks, wdesc + (uint64_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4),
+                       IDESC1, ks > 0 ? 1u : 0u);
+          umma_commit_1t(KN_FULL(s));
+          umma_commit_1t(A_EMPTY);
+        }
+        __syncwarp();
+        PP_T(2);
+      }
+    }
+  }
+
+  // ---- epilogue: merge the 12 token-warps' states per head and emit the record -------------------
+  __syncthreads();
+  float* acc_s = reinterpret_cast<float*>(v_s);                   // [3 groups][16][128]
+  if (warp < PP_CONS_WARPS) {
+    const int g = warp >> 2, quad = warp & 3, m = quad * 32 + lane;
+#pragma unroll
+    for (int h = 0; h < GQA; ++h) {
+      const float l = warp_sum(run_l[h]);
+      if (lane == 0) { m_s[16 * g + 4 * quad + h] = run_m[h]; l_s[16 * g + 4 * quad + h] = l; }
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc_s[(16 * g + j) * HD + m] = acc[j];
+  }
+  __syncthreads();
+  if (tid < 256) {
+    const int half = tid >> 7, m = tid & 127;
+    const float ch = __half2float(reinterpret_cast<const __half*>(sq.v_ch)[kv * HD + m]);
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int h = 2 * half + hh;
+      float M = neg_inf();
+#pragma unroll
+      for (int e = 0; e < 12; ++e) M = fmaxf(M, m_s[16 * (e >> 2) + 4 * (e & 3) + h]);
+      float L = 0.f, a = 0.f;
+#pragma unroll
+      for (int e = 0; e < 12; ++e) {
+        const int idx = 16 * (e >> 2) + 4 * (e & 3) + h;
+        const float mv = m_s[idx];
+        const float wt = (mv == neg_inf()) ? 0.f : exp2f((mv - M) * LOG2E);
+        L = fmaf(wt, l_s[idx], L);
+        a = fmaf(wt, acc_s[idx * HD + m], a);
+      }
+      float* rec = rec_base + h * PART;
+      if (m == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
+      rec[4 + m] = a * ch;
+    }
+  }
+  if (tid == 0 && *abort_s && p.status) atomicExch(p.status, 1);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == PP_UNPACK_WARP0) tmem_dealloc(tmem_base, PP_TMEM_COLS);
+#ifdef SHARD_TC_DEBUG
+  if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 49] += clock64() - pp_kstart__;
+  if (g_pp_debug && tid < 48)
+    g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + tid] += reinterpret_cast<long long*>(smem + pp_smem_bytes(NW) - 1024 - 512)[tid];
+#endif
+}
+
+template <int NW>
+static int launch_pipe_one(const DecodeParams& p, dim3 grid, cudaStream_t st) {
+  constexpr int SMEM = pp_smem_bytes(NW);
+  static_assert(SMEM >= (2 * GQA * HD + 256 + PP_WARPS * GQA * 130) * 4, "row path scratch must fit");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_partial_pipe_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  decode_partial_pipe_kernel<NW><<<grid, PP_THREADS, SMEM, st>>>(p);
+  return 0;
+}
+
+int launch_partial_pipe(const DecodeParams& p, dim3 grid, cudaStream_t st) {
+  switch (p.sh.rank / 32) {
+    case 1: return launch_pipe_one<1>(p, grid, st);
+    case 2: return launch_pipe_one<2>(p, grid, st);
+    case 3: return launch_pipe_one<3>(p, grid, st);
+    case 4: return launch_pipe_one<4>(p, grid, st);
+    case 5: return launch_pipe_one<5>(p, grid, st);
+    default: return launch_pipe_one<6>(p, grid, st);
+  }
+}
+
+}  // namespace shard
