@@ -220,15 +220,29 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     T, L = args.ctx, args.layers
-    n_comp = T - SINK - WIN
     K, W = args.steps, max(args.warmup, 3)
     seqs_per_gpu = args.seqs
+    cfg3 = args.workload == "cfg3"
+    if cfg3:
+        T = 8192 if args.ctx == 32768 else args.ctx
+        total_seqs = 64
+        if total_seqs % world:
+            raise SystemExit("cfg3 needs a GPU count that divides 64")
+        seqs_per_gpu = total_seqs // world
+    n_comp = T - SINK - WIN
 
     t0 = time.perf_counter()
-    caches = [build_cache(T, L, 100 + 1000 * (rank * seqs_per_gpu + s), dev) for s in range(seqs_per_gpu)]
+    if cfg3:
+        # 64 x 32 layer caches: random codes built on the device (decode cost is data independent)
+        from shard_b200 import synth as _synth
+        caches = [_synth.random_cache(n_comp, L, dev, 5000 + 100 * (rank * seqs_per_gpu + s))
+                  for s in range(seqs_per_gpu)]
+        compress_s, ratio = None, None
+    else:
+        caches = [build_cache(T, L, 100 + 1000 * (rank * seqs_per_gpu + s), dev) for s in range(seqs_per_gpu)]
+        compress_s = sum(c.compress_seconds for c in caches) / len(caches)
+        ratio = caches[0].clean_compress_ratio()
     build_s = time.perf_counter() - t0
-    compress_s = sum(c.compress_seconds for c in caches) / len(caches)
-    ratio = caches[0].clean_compress_ratio()
 
     bd = BatchedDecoder(caches, stream_capacity=2 * (K + W) + 8)
     total = K + W
@@ -288,7 +302,7 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end through the public API, host buffers ----------------------------
-    e2e_steps = min(K, 32)
+    e2e_steps = min(K, 4 if cfg3 else 32)
     cache = caches[0]
     hq = torch.randn(L, 1, N_Q, 1, HD).half().pin_memory()
     hk = torch.randn(L, 1, N_KV, 1, HD).half().pin_memory()
@@ -301,16 +315,17 @@ def run_ours(args):
     inv = cache._rope_inv_freq
 
     def e2e_step(pos):
-        dq.copy_(hq, non_blocking=True)
-        dk.copy_(hk, non_blocking=True)
-        dv.copy_(hv, non_blocking=True)
-        cache._fused_decode_update = True
-        for li in range(L):
-            layer = cache.layers[li]
-            layer.update(dk[li], dv[li])
-            dout[li] = fused_attention_compressed(dq[li], layer, pos, inv, None)
-        cache._fused_decode_update = False
-        hout.copy_(dout, non_blocking=True)
+        for c in caches:
+            dq.copy_(hq, non_blocking=True)
+            dk.copy_(hk, non_blocking=True)
+            dv.copy_(hv, non_blocking=True)
+            c._fused_decode_update = True
+            for li in range(L):
+                layer = c.layers[li]
+                layer.update(dk[li], dv[li])
+                dout[li] = fused_attention_compressed(dq[li], layer, pos, inv, None)
+            c._fused_decode_update = False
+            hout.copy_(dout, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     pos = cache.layers[0].get_seq_length()
@@ -341,12 +356,14 @@ def run_ours(args):
         achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": us, "unit": "us", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong" if cfg3 else "weak",
+            "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
             "config": {
-                "workload": f"cfg2: Llama-3.1-8B geometry ({N_Q}/{N_KV} heads, head_dim {HD}), {T}-token "
-                            f"context, {L} layers, {seqs_per_gpu} sequence(s) per GPU, 8-bit stream grows "
-                            f"{W}->{W + K} tokens",
+                "workload": (f"{args.workload}: Llama-3.1-8B geometry ({N_Q}/{N_KV} heads, head_dim {HD}), "
+                             f"{T}-token context, {L} layers, {seqs_per_gpu} sequence(s) per GPU"
+                             + (f" ({seqs_per_gpu * world} in total, random codes)" if cfg3 else "")
+                             + f", 8-bit stream grows {W}->{W + K} tokens"),
                 "l2": "inputs larger than L2: one step touches %.0f MB of cache per GPU"
                       % (bytes_ls * L * seqs_per_gpu / 1e6),
                 "parallelism": "batch-sharded, no communication" if world > 1 else "single GPU",
@@ -362,11 +379,11 @@ def run_ours(args):
                          "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": None,
                          "us_per_launch": kern_ms * 1e3,
                          "tensor_frac": (flops_ls * seqs_per_gpu / (kern_ms * 1e-3) / 1e12) / tf_peak},
-            "e2e": {"value": e2e_ms * 1e3 / L, "unit": "us",
-                    "h2d_bytes_per_step": L * (N_Q + 2 * N_KV) * HD * 2,
-                    "d2h_bytes_per_step": L * N_Q * HD * 2,
+            "e2e": {"value": e2e_ms * 1e3 / (L * n_seq_total), "unit": "us",
+                    "h2d_bytes_per_step": seqs_per_gpu * L * (N_Q + 2 * N_KV) * HD * 2,
+                    "d2h_bytes_per_step": seqs_per_gpu * L * N_Q * HD * 2,
                     "ms_per_step": e2e_ms, "api": "Cache.layers[i].update + fused_attention_compressed"},
-            "gpu_launches": K * (1 + 3 * L),
+            "gpu_launches": K * (1 + (4 if bd.S > 1 else 3) * L),
             "clocks": clocks,
         }
         if args.cpu_baseline:
@@ -374,6 +391,112 @@ def run_ours(args):
             line["cpu_baseline"] = {"value": sec * 1e6, "unit": "us", "cores": cores, "kind": "port",
                                     "sample": f"3 layer-steps (1 warm-up) of one layer, n_comp={n_comp}, "
                                               "numpy port of the reference's CPU path"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_seqsplit(args):
+    """cfg4: one long sequence, its compressed middle cut into contiguous token ranges (one per
+    GPU); every rank decodes its range, the per-head (max, sum-exp, acc) records are all-gathered
+    over NCCL and merged by the log-sum-exp kernel.  Rank 0 also owns sink, window and stream."""
+    import torch
+    import torch.distributed as dist
+    from shard_b200 import ops, synth
+    from shard_b200.attention import decode_layer
+    from shard_b200.parallel import split_ranges
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    T = 131072 if args.ctx == 32768 else args.ctx
+    L, K, W = args.layers, args.steps, max(args.warmup, 3)
+    n_comp = T - SINK - WIN
+    begin, end = split_ranges(n_comp, world)[rank]
+    first = rank == 0
+    cache = synth.random_cache(end - begin, L, dev, 9000, compress_start=SINK + begin,
+                               n_sink=SINK if first else 0, n_win=WIN if first else 0)
+    total = K + W
+    g = torch.Generator(device=dev).manual_seed(77)          # same queries on every rank
+    q_pool = torch.randn(total, L, 1, N_Q, 1, HD, generator=g, device=dev).half()
+    k_pool = torch.randn(total, L, 1, N_KV, 1, HD, generator=g, device=dev).half()
+    v_pool = torch.randn(total, L, 1, N_KV, 1, HD, generator=g, device=dev).half()
+    parts = torch.empty(world, N_Q, 132, dtype=torch.float32, device=dev)
+    part = torch.empty(N_Q, 132, dtype=torch.float32, device=dev)
+    out = torch.empty(L, N_Q, HD, dtype=torch.float16, device=dev)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K * L)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step(j, timed):
+        pos = T + j
+        cache._fused_decode_update = True
+        for li in range(L):
+            layer = cache.layers[li]
+            if first:
+                layer.update(k_pool[j, li], v_pool[j, li])           # stream append (rank 0 owns the stream)
+            e = ev[(j - W) * L + li] if timed else None
+            if e: e[0].record()
+            decode_layer(q_pool[j, li], layer, pos, partial_out=True, with_fp16_segments=first, out=part)
+            if e: e[1].record()
+            if world > 1:
+                dist.all_gather_into_tensor(parts.view(-1), part.view(-1))
+            else:
+                parts[0].copy_(part)
+            ops.lse_merge(parts, out=out[li])
+            if e: e[2].record()
+        cache._fused_decode_update = False
+
+    for j in range(W):
+        step(j, False)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for j in range(W, W + K):
+        step(j, True)
+    ev1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = ev0.elapsed_time(ev1)
+    dec_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / K
+    mrg_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / K
+    vals = torch.tensor([ms_total, dec_ms, mrg_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    ms_total, dec_ms, mrg_ms = (float(x) for x in vals.tolist())
+    ms_per_step = ms_total / K
+    if rank == 0:
+        hbm_peak, tf_peak, peak_kind = measured_peaks()
+        n_local = end - begin
+        bytes_ls = algorithmic_bytes(n_local, W + K // 2)
+        line = {
+            "metric": METRIC, "value": ms_per_step * 1e3 / L, "unit": "us", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"cfg4: one {T}-token sequence, {L} layers, compressed middle split into "
+                                   f"{world} contiguous token range(s) (random codes), log-sum-exp merge over NCCL",
+                       "l2": "inputs larger than L2: one step touches %.0f MB of cache per GPU" % (bytes_ls * L / 1e6),
+                       "parallelism": f"sequence-split x{world}"},
+            "decode_us_per_layer": dec_ms * 1e3 / L, "merge_us_per_layer": mrg_ms * 1e3 / L,
+            "merge_overhead_frac": mrg_ms / max(dec_ms + mrg_ms, 1e-9),
+            "hbm_gbs_per_gpu": bytes_ls * L / (ms_per_step * 1e-3) / 1e9,
+            "roofline": {"kernel": "decode_partial_pipe_kernel + decode_combine_kernel", "bound": "hbm",
+                         "achieved": bytes_ls / (dec_ms / L * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": bytes_ls / (dec_ms / L * 1e-3) / 1e9 / hbm_peak, "peak_kind": peak_kind, "traffic": None},
+            "e2e": {"value": None, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": K * (1 + L * (4 if first else 3)), "clocks": clocks,
+        }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -387,11 +510,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=32768)
     ap.add_argument("--layers", type=int, default=32)
-    ap.add_argument("--seqs", type=int, default=1, help="sequences per GPU")
+    ap.add_argument("--seqs", type=int, default=1, help="sequences per GPU (cfg2)")
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4"],
+                    help="cfg2: one 32K sequence per GPU (headline); cfg3: 64 x 8K sequences sharded by batch; "
+                         "cfg4: one 131072-token sequence split by token range, merged over NCCL")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "cfg4":
+        run_seqsplit(args)
     else:
         run_ours(args)
 

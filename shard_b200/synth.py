@@ -64,3 +64,54 @@ def make_token(seed: int, device="cpu", nkv: int = N_KV, n_q: int = N_Q, hd: int
     v = torch.randn(1, nkv, 1, hd, generator=g, device=dev)
     q = torch.randn(1, n_q, 1, hd, generator=g, device=dev)
     return k.half(), v.half(), q.half()
+
+
+def random_compressed_layer(n_comp, device, seed, compress_start=4, n_sink=4, n_win=64, rank=192, nkv=N_KV,
+                            hd=HEAD_DIM):
+    """A compressed layer with random codes, built directly on `device` (no prefill, no
+    compression).  Decode cost does not depend on code values, so the multi-GPU
+    benchmark workloads use this to set up many / very long caches quickly.  Returns the
+    per-layer tensor dictionary in the product's format (kernel-side weights attached)."""
+    from .cache import attach_kernel_format
+    dev = torch.device(device)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    p = nkv * hd
+    basis_q = torch.randint(-127, 128, (p, rank), generator=g, device=dev, dtype=torch.int8)
+    basis_scale = (0.08 / 127 * (0.5 + torch.rand(rank, generator=g, device=dev))).half()
+    decay = torch.exp(-0.01 * torch.arange(rank, device=dev, dtype=torch.float32))
+    gc = {
+        "k_coeffs": torch.randint(0, 256, (n_comp * rank // 2,), generator=g, device=dev, dtype=torch.uint8),
+        "k_coeff_scale": (decay * 0.4).half(),
+        "k_coeffs_shape": (n_comp, rank),
+        "k_basis_q": basis_q,
+        "k_basis_scale": basis_scale,
+        "k_basis_f16": (basis_q.half() * basis_scale).contiguous(),
+        "k_mean": (torch.randn(p, generator=g, device=dev) * 0.1).half(),
+        "v_indices_u8": torch.randint(0, 256, (nkv, n_comp, hd // 4), generator=g, device=dev, dtype=torch.uint8),
+        "v_centroids_f16": (torch.randn(256, 4, generator=g, device=dev) * 0.4).half(),
+        "v_ch_f16": (0.5 + 3 * torch.rand(nkv, hd, generator=g, device=dev)).half(),
+        "sink_k": torch.randn(1, nkv, n_sink, hd, generator=g, device=dev).half(),
+        "sink_v": torch.randn(1, nkv, n_sink, hd, generator=g, device=dev).half(),
+        "win_k": torch.randn(1, nkv, n_win, hd, generator=g, device=dev).half(),
+        "win_v": torch.randn(1, nkv, n_win, hd, generator=g, device=dev).half(),
+        "n_compress": n_comp, "batch": 1, "compress_start": compress_start,
+    }
+    gc["k_mean_f16"] = gc["k_mean"]
+    gc["v_packed"] = gc["v_indices_u8"].view(-1)
+    attach_kernel_format(gc, nkv)
+    return gc
+
+
+def random_cache(n_comp, layers, device, seed0, **kw):
+    """A `Cache` whose layers are `random_compressed_layer`s (already 'compressed')."""
+    from .cache import Cache
+    cache = Cache(num_layers=layers, rope_inv_freq=rope_inv_freq(), device=str(device))
+    cache._streaming = True
+    cache._compressed = True
+    for li in range(layers):
+        layer = cache.layers[li]
+        layer._gpu_compressed = random_compressed_layer(n_comp, device, seed0 + li, **kw)
+        layer._prefilled = True
+        layer._needs_decompress = True
+        layer._seq_len = kw.get("compress_start", 4) + n_comp + kw.get("n_win", 64)
+    return cache

@@ -1,0 +1,63 @@
+"""Two-GPU test of the sequence-split decode: every rank attends to its slice of the compressed
+middle, the per-head (max, sum-exp, acc) records travel through NCCL, and the merged result
+equals single-GPU attention over the whole cache.  Skipped on boxes with fewer than 2 GPUs."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from conftest import REPO
+
+pytestmark = pytest.mark.gpu
+
+_WORKER = r'''
+import os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, os.path.join(sys.argv[1], "tests"))
+from gpu_helpers import FakeCache, FakeLayer, gc_to_device, random_gc, random_query
+from oracle import shard_oracle as O
+from conftest import tol_ok
+from shard_b200.cache import attach_kernel_format
+from shard_b200.parallel import seqsplit_decode, shard_layer_tokens
+from shard_b200.attention import decode_layer
+
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+gc_np = random_gc(5000, seed=3)
+q_np = random_query(seed=4)
+inv = torch.from_numpy(O.default_inv_freq())
+full = FakeLayer(gc_to_device(gc_np, f"cuda:{rank}"), FakeCache(inv))
+q = torch.from_numpy(q_np).to(f"cuda:{rank}").view(1, 32, 1, 128)
+whole = decode_layer(q, full, 5100).clone()
+sub = shard_layer_tokens(full._gpu_compressed, rank, world)
+attach_kernel_format(sub, 8)
+mine = FakeLayer(sub, FakeCache(inv))
+out = seqsplit_decode(q, mine, 5100)
+torch.cuda.synchronize()
+got, ref = out.cpu().numpy()[0, :, 0, :], whole.cpu().numpy()
+assert np.abs(got.astype(np.float32) - ref.astype(np.float32)).max() <= 2e-3
+exact, *_ = O.attention_exact(q_np, gc_np, 5100, O.default_inv_freq())
+assert tol_ok(got, exact, atol=1.5e-3, rtol=5e-3)
+gathered = [None] * world
+dist.all_gather_object(gathered, got.tobytes())
+assert all(x == gathered[0] for x in gathered)      # bitwise identical on every rank
+dist.destroy_process_group()
+print("ok", rank)
+'''
+
+
+def test_sequence_split_decode_over_nccl(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(29700 + os.getpid() % 200),
+               WORLD_SIZE="2")
+    procs = [subprocess.Popen([sys.executable, str(script), REPO], env=dict(env, RANK=str(r), LOCAL_RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE) for r in range(2)]
+    for p in procs:
+        out, err = p.communicate(timeout=300)
+        assert p.returncode == 0, err.decode()[-3000:]
