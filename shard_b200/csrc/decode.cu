@@ -29,35 +29,32 @@ constexpr int DEC_THREADS = 128;
 constexpr int DEC_WARPS = 4;
 constexpr int TILE_TOK = 16;           // tokens per warp tile of the mma.sync kernel
 constexpr int MMA_CTA_SLOTS = 148 * 3; // resident CTAs of the mma.sync kernel on a B200
-constexpr int TC_TILE_TOK = 128;       // tokens per CTA tile of the tcgen05 kernel
-constexpr int TC_CTA_SLOTS = 148 * 2;  // two resident CTAs per SM
+constexpr int TC_TILE_TOK = 128;       // tokens per tile of the tcgen05 kernel
 constexpr int PIPE_CTA_SLOTS = 148;    // the pipelined kernel keeps one CTA per SM
 constexpr int WS_HEADER_BYTES = 16;    // status word + padding in front of the partial records
 
-// implemented in decode_tc.cu
-size_t tc_wprep_bytes(int nkv, int rank);
-int launch_prepare_tc(const void* basis, const void* cscale, const void* mean, int nkv, int rank, void* out,
-                      cudaStream_t st);
-int launch_partial_tc(const DecodeParams& p, dim3 grid, cudaStream_t st);
 // implemented in decode_pipe.cu
+size_t pipe_wprep_bytes(int nkv, int rank);
+int launch_prepare_pipe(const void* basis, const void* cscale, const void* mean, int nkv, int rank, void* out,
+                        cudaStream_t st);
 int launch_partial_pipe(const DecodeParams& p, dim3 grid, cudaStream_t st);
 
-__host__ __device__ inline size_t tc_blob_bytes(int nkv, int rank) {
-  return (size_t)nkv * (((rank + 63) / 64) * 16384 + 512);
+__host__ __device__ inline size_t pipe_blob_bytes(int nkv, int rank) {
+  return (size_t)nkv * (((rank + 16 + 63) / 64) * 16384);
 }
 
 struct DecodePlan {
   int n_chunks, tiles_per_chunk, tiles_rem, n_fp16_ctas, n_stream_ctas, n_parts;
 };
 
-// Which kernel walks the compressed middle: the pipelined tcgen05 kernel (default), or one of
-// the two earlier kernels kept for A/B timing (environment SHARD_B200_DECODE=tc1 | mma).
-enum DecodeMode { MODE_PIPE = 0, MODE_TC1 = 1, MODE_MMA = 2 };
+// Which kernel walks the compressed middle: the pipelined tcgen05 kernel (default), or the
+// earlier mma.sync kernel kept for A/B timing (environment SHARD_B200_DECODE=mma).
+enum DecodeMode { MODE_PIPE = 0, MODE_MMA = 2 };
 static DecodeMode decode_mode() {
   static int mode = -1;
   if (mode < 0) {
     const char* e = getenv("SHARD_B200_DECODE");
-    mode = (e && e[0] == 'm') ? MODE_MMA : (e && e[0] == 't') ? MODE_TC1 : MODE_PIPE;
+    mode = (e && e[0] == 'm') ? MODE_MMA : MODE_PIPE;
   }
   return (DecodeMode)mode;
 }
@@ -78,15 +75,13 @@ static DecodePlan make_plan(const ShardDecodeShape& sh, int batch) {
     pl.tiles_per_chunk = n_tiles / chunks;
     pl.tiles_rem = n_tiles % chunks;
   } else if (n_tiles > 0) {
-    const bool tc = mode == MODE_TC1;
-    const int slots = tc ? TC_CTA_SLOTS : MMA_CTA_SLOTS;
     int tpc;
-    if (groups >= slots / 2) {
-      tpc = tc ? 8 : 64;
+    if (groups >= MMA_CTA_SLOTS / 2) {
+      tpc = 64;
     } else {
-      const int chunks = slots / groups;
+      const int chunks = MMA_CTA_SLOTS / groups;
       tpc = (n_tiles + chunks - 1) / chunks;
-      if (!tc && tpc < DEC_WARPS) tpc = DEC_WARPS;
+      if (tpc < DEC_WARPS) tpc = DEC_WARPS;
     }
     pl.tiles_per_chunk = tpc;
     pl.n_chunks = (n_tiles + tpc - 1) / tpc;
@@ -204,7 +199,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) decode_partial_kernel(const __
   // ---- stage per-CTA constants -------------------------------------------
   if (is_mid) {
     const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(sq.k_wprep) +
-                                                      tc_blob_bytes(sh.nkv, R) + (size_t)kv * W_BYTES);
+                                                      pipe_blob_bytes(sh.nkv, R) + (size_t)kv * W_BYTES);
     uint4* dst = reinterpret_cast<uint4*>(smem);
     for (int i = tid; i < W_BYTES / 16; i += DEC_THREADS) dst[i] = src[i];
     const uint2* cb_src = reinterpret_cast<const uint2*>(sq.v_centroids);
@@ -476,12 +471,12 @@ extern "C" int shard_b200_phase_table(int32_t compress_start, int32_t pos_q, int
   return SHARD_OK;
 }
 
-// blob = [tcgen05 layout: nkv x (W core matrices + fp32 mean)] [mma.sync fragment layout]
+// blob = [tcgen05 operand layout: nkv x W atoms (mean folded in)] [mma.sync fragment layout]
 static size_t mma_wprep_bytes(int nkv, int rank) { return (size_t)nkv * (rank / 16 + 1) * 16 * 32 * 8; }
 
 extern "C" size_t shard_b200_wprep_bytes(int32_t nkv, int32_t rank) {
   if (nkv < 1 || rank < 32 || rank > 192 || (rank % 32)) return 0;
-  return tc_wprep_bytes(nkv, rank) + mma_wprep_bytes(nkv, rank);
+  return pipe_wprep_bytes(nkv, rank) + mma_wprep_bytes(nkv, rank);
 }
 
 extern "C" int shard_b200_decode_prepare(const void* basis_f16, const void* coeff_scale, const void* mean_f16,
@@ -489,11 +484,12 @@ extern "C" int shard_b200_decode_prepare(const void* basis_f16, const void* coef
   if (!basis_f16 || !coeff_scale || !mean_f16 || !wprep_out) return SHARD_E_ARG;
   if (nkv < 1 || rank < 32 || rank > 192 || (rank % 32)) return SHARD_E_ARG;
   if ((uintptr_t)wprep_out & 15) return SHARD_E_ALIGN;
-  launch_prepare_tc(basis_f16, coeff_scale, mean_f16, nkv, rank, wprep_out, (cudaStream_t)stream);
+  int prc = launch_prepare_pipe(basis_f16, coeff_scale, mean_f16, nkv, rank, wprep_out, (cudaStream_t)stream);
+  if (prc) return prc;
   const int total = nkv * (rank / 16 + 1) * 16 * 32;
   decode_prepare_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
       (const __half*)basis_f16, (const __half*)coeff_scale, (const __half*)mean_f16, nkv, rank,
-      (uint2*)((unsigned char*)wprep_out + tc_wprep_bytes(nkv, rank)));
+      (uint2*)((unsigned char*)wprep_out + pipe_wprep_bytes(nkv, rank)));
   SHARD_CHECK_LAUNCH();
   return SHARD_OK;
 }
@@ -574,8 +570,6 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
   if (decode_mode() == MODE_PIPE) {
     if (batch == 1 && ((uintptr_t)p.one.k_coeffs & 15)) return SHARD_E_ALIGN;
     rc = launch_partial_pipe(p, grid, st);
-  } else if (decode_mode() == MODE_TC1) {
-    rc = launch_partial_tc(p, grid, st);
   } else {
     switch (sh.rank / 32) {
       case 1: rc = launch_partial<1>(p, grid, st); break;

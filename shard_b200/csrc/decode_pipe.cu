@@ -32,19 +32,20 @@ constexpr int PP_UNPACK_WARP0 = 12;
 constexpr int PP_WARPS = 16;
 constexpr int PP_THREADS = PP_WARPS * 32;
 constexpr int PP_TMEM_COLS = 512;
-constexpr int PP_COL_A = 384;         // A operand slot, R/2 columns
+constexpr int PP_COL_A = 384;         // A operand slot: R/2 coefficient columns + 8 constant columns (1, 0, ...)
 constexpr int PP_COL_S = 64;          // within a stage
 constexpr int PP_COL_O = 80;
-constexpr int PP_V_BYTES = 32768, PP_P_BYTES = 4096, PP_Q_BYTES = 4096, PP_CB_BYTES = 2048, PP_MEAN_BYTES = 512;
+constexpr int PP_V_BYTES = 32768, PP_P_BYTES = 4096, PP_Q_BYTES = 4096, PP_CB_BYTES = 2048;
 #ifdef SHARD_TC_DEBUG
 constexpr int PP_MISC_BYTES = 1024 + 1024 + 512;   // + per-role timing accumulators
 #else
 constexpr int PP_MISC_BYTES = 1024 + 1024;   // state + barriers, and slack for 1 KB alignment
 #endif
 
-__host__ __device__ constexpr int pp_w_bytes(int nw) { return ((nw + 1) / 2) * 16384; }
+// W holds R + 16 contraction positions (the last 16 carry the mean), in 64-position atoms of 16 KB
+__host__ __device__ constexpr int pp_w_bytes(int nw) { return ((32 * nw + 16 + 63) / 64) * 16384; }
 __host__ __device__ constexpr int pp_smem_bytes(int nw) {
-  return pp_w_bytes(nw) + PP_STAGES * (PP_V_BYTES + PP_P_BYTES) + PP_Q_BYTES + PP_CB_BYTES + PP_MEAN_BYTES + PP_MISC_BYTES;
+  return pp_w_bytes(nw) + PP_STAGES * (PP_V_BYTES + PP_P_BYTES) + PP_Q_BYTES + PP_CB_BYTES + PP_MISC_BYTES;
 }
 
 // single-thread forms (the caller is one elected thread)
@@ -92,7 +93,7 @@ template <int NW>  // rank / 32
 __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(const __grid_constant__ DecodeParams p) {
   constexpr int R = NW * 32;
   constexpr int KC = R / 8;          // 32-bit words of nibbles per coefficient row
-  constexpr int KSTEPS = R / 16;
+  constexpr int KSTEPS = R / 16 + 1;   // + one step whose A columns are (1, 0, ...) and whose W slice is the mean
   constexpr int W_BYTES = pp_w_bytes(NW);
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -102,8 +103,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   unsigned char* p_s = v_s + PP_STAGES * PP_V_BYTES;               // [3] P operands [16 x 128 tok]
   unsigned char* q_s = p_s + PP_STAGES * PP_P_BYTES;               // Q operand [16 x 128]
   uint2* cbv = reinterpret_cast<uint2*>(q_s + PP_Q_BYTES);         // V codebook
-  float* mean_s = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(cbv) + PP_CB_BYTES);
-  float* misc = mean_s + 128;
+  float* misc = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(cbv) + PP_CB_BYTES);
   float* alpha_s = misc;                                           // [3][16]
   float* m_s = misc + 48;                                          // [3][16]
   float* l_s = misc + 96;                                          // [3][16]
@@ -154,11 +154,10 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
 
   // ---- one-time setup -------------------------------------------------------------------
   {
-    const unsigned char* blob = reinterpret_cast<const unsigned char*>(sq.k_wprep) + (size_t)kv * (W_BYTES + PP_MEAN_BYTES);
+    const unsigned char* blob = reinterpret_cast<const unsigned char*>(sq.k_wprep) + (size_t)kv * W_BYTES;
     const uint4* src = reinterpret_cast<const uint4*>(blob);
     uint4* dst = reinterpret_cast<uint4*>(w_s);
     for (int i = tid; i < W_BYTES / 16; i += PP_THREADS) dst[i] = src[i];
-    if (tid < 128) mean_s[tid] = reinterpret_cast<const float*>(blob + W_BYTES)[tid];
     if (tid < 256) cbv[tid] = reinterpret_cast<const uint2*>(sq.v_centroids)[tid];
     uint4* z = reinterpret_cast<uint4*>(p_s);
     for (int i = tid; i < (PP_STAGES * PP_P_BYTES + PP_Q_BYTES) / 16; i += PP_THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -221,6 +220,9 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   if (warp < PP_CONS_WARPS) {
     // =============================== consumer groups ======================================
     const int g = warp >> 2, quad = warp & 3, m = quad * 32 + lane;
+    // the four MMA-issuing threads of the CTA (one per consumer group + one unpack warp) sit on
+    // four different warp schedulers: group g issues from its warp g + 1, the unpack side from warp 12
+    const int issuer_quad = g + 1;
     const uint32_t T_g = tmem_base + (uint32_t)(128 * g);
     const uint32_t lane_T = T_g + ((uint32_t)(quad * 32) << 16);
     constexpr uint32_t IDESC2 = umma_idesc(128, 16, false, false);
@@ -245,7 +247,11 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       const int tok = min(t0 + m, sh.tok_end - 1);
       const bool valid = (t0 + m) < sh.tok_end;
       const uint4* prow = reinterpret_cast<const uint4*>(phase_tab + (size_t)(tok - sh.tok_begin) * 64);
-      uint4 pc = prow[0], ps = prow[8];          // cos words 0-31 (uint4 0-7), sin words 32-63 (uint4 8-15)
+      // cos/sin of the row, one uint4 (4 pairs of pairs) per chunk; kept three chunks ahead of use
+      uint4 pc[8], ps[8];
+      pc[0] = prow[0]; ps[0] = prow[8];
+      pc[1] = prow[1]; ps[1] = prow[9];
+      pc[2] = prow[2]; ps[2] = prow[10];
 
       PP_T(0);
       bad |= !mbar_wait(KN_FULL(g), par, abort_s);
@@ -262,19 +268,17 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
         uint32_t cr[8], dr[8];
         tmem_ld_x8(lane_T + 8 * ch, cr);
         tmem_ld_x8(lane_T + 64 + 8 * ch, dr);
-        const uint32_t cos2[4] = {pc.x, pc.y, pc.z, pc.w};
-        const uint32_t sin2[4] = {ps.x, ps.y, ps.z, ps.w};
-        if (ch < 7) { pc = prow[ch + 1]; ps = prow[8 + ch + 1]; }
+        if (ch + 3 < 8) { pc[ch + 3] = prow[ch + 3]; ps[ch + 3] = prow[8 + ch + 3]; }
+        const uint32_t cos2[4] = {pc[ch].x, pc[ch].y, pc[ch].z, pc[ch].w};
+        const uint32_t sin2[4] = {ps[ch].x, ps[ch].y, ps[ch].z, ps[ch].w};
         PP_T(13);
         tmem_wait_ld();
         PP_T(14);
         uint32_t oc[4], od[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float2 mc = *reinterpret_cast<const float2*>(mean_s + 8 * ch + 2 * j);
-          const float2 md = *reinterpret_cast<const float2*>(mean_s + 64 + 8 * ch + 2 * j);
-          const __half2 c2 = __floats2half2_rn(__uint_as_float(cr[2 * j]) + mc.x, __uint_as_float(cr[2 * j + 1]) + mc.y);
-          const __half2 d2 = __floats2half2_rn(__uint_as_float(dr[2 * j]) + md.x, __uint_as_float(dr[2 * j + 1]) + md.y);
+          const __half2 c2 = __floats2half2_rn(__uint_as_float(cr[2 * j]), __uint_as_float(cr[2 * j + 1]));
+          const __half2 d2 = __floats2half2_rn(__uint_as_float(dr[2 * j]), __uint_as_float(dr[2 * j + 1]));
           const __half2 cs = as_half2(cos2[j]), sn = as_half2(sin2[j]);
           oc[j] = as_u32(__hfma2(c2, cs, __hneg2(__hmul2(d2, sn))));   // c cos - d sin
           od[j] = as_u32(__hfma2(d2, cs, __hmul2(c2, sn)));            // d cos + c sin
@@ -301,7 +305,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       tc_fence_before();
       bad = named_bar_or(1 + g, 128, bad || *abort_s);
       if (bad) break;                                   // uniform over the group
-      if (quad == 0 && lane == 0) {
+      if (quad == issuer_quad && lane == 0) {
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
@@ -340,7 +344,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       tc_fence_before();
       bad = named_bar_or(1 + g, 128, bad || *abort_s);
       if (bad) break;                                   // uniform over the group
-      if (quad == 0 && lane == 0) {
+      if (quad == issuer_quad && lane == 0) {
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
@@ -379,6 +383,11 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     const uint64_t wdesc = smem_desc_sw128(smem_u32(w_s), 16, 1024);
     const int quad = warp - PP_UNPACK_WARP0, m = quad * 32 + lane;
     const uint32_t lane_A = tmem_base + PP_COL_A + ((uint32_t)(quad * 32) << 16);
+    {
+      // constant part of the A operand: position R is 1.0 (it multiplies the mean slice of W)
+      const uint32_t ones[8] = {0x00003C00u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+      tmem_st_x8(lane_A + R / 2, ones);
+    }
     uint4 x[NW];
     {
       const int tok = min(sh.tok_begin + tile_lo * 128 + m, sh.tok_end - 1);
@@ -403,10 +412,11 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
         uint32_t o[16];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
+          const uint32_t hi = wv[e] >> 8;
           o[4 * e + 0] = nib2half2_tc(wv[e]);          // ranks 8c+0, 8c+4 of word c = 4i+e
-          o[4 * e + 1] = nib2half2_tc(wv[e] >> 4);     //       8c+1, 8c+5
-          o[4 * e + 2] = nib2half2_tc(wv[e] >> 8);     //       8c+2, 8c+6
-          o[4 * e + 3] = nib2half2_tc(wv[e] >> 12);    //       8c+3, 8c+7
+          o[4 * e + 1] = nib2half2_hi(wv[e]);          //       8c+1, 8c+5
+          o[4 * e + 2] = nib2half2_tc(hi);             //       8c+2, 8c+6
+          o[4 * e + 3] = nib2half2_hi(hi);             //       8c+3, 8c+7
         }
         tmem_st_x16(lane_A + 16 * i, o);
       }
@@ -486,6 +496,46 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   if (g_pp_debug && tid < 48)
     g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + tid] += reinterpret_cast<long long*>(smem + pp_smem_bytes(NW) - 1024 - 512)[tid];
 #endif
+}
+
+// Prepared weights: per KV head, W = basis * coefficient scale as fp16 in the K-major, 128-byte
+// swizzled operand layout (atoms of 64 contraction positions x 128 rows).  Position kk = 8c + p
+// holds rank 8c + perm[p] (the order in which the unpack step emits the nibbles of word c);
+// position R holds the mean, positions R+1 .. R+15 are zero.
+__global__ void __launch_bounds__(256) decode_prepare_pipe_kernel(const __half* __restrict__ basis,
+                                                                  const __half* __restrict__ cscale,
+                                                                  const __half* __restrict__ mean, int nkv, int rank,
+                                                                  unsigned char* __restrict__ out) {
+  const int kpos = rank + 16;
+  const int w_bytes = ((kpos + 63) / 64) * 16384;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= nkv * HD * kpos) return;
+  const int kk = idx % kpos;
+  const int j = (idx / kpos) % HD;
+  const int kv = idx / (kpos * HD);
+  const int c = kk >> 3, pp = kk & 7;
+  __half v = __float2half(0.f);
+  if (kk < rank) {
+    const int perm = ((pp & 1) << 2) | (pp >> 1);                // 0,4,1,5,2,6,3,7
+    const int r = 8 * c + perm;
+    v = __hmul(basis[(size_t)(kv * HD + j) * rank + r], cscale[r]);
+  } else if (kk == rank) {
+    v = mean[kv * HD + j];
+  }
+  *reinterpret_cast<__half*>(out + (size_t)kv * w_bytes + (c >> 3) * 16384 + (j >> 3) * 1024 + (j & 7) * 128 +
+                             (((c & 7) ^ (j & 7)) << 4) + pp * 2) = v;
+}
+
+size_t pipe_wprep_bytes(int nkv, int rank) { return (size_t)nkv * (((rank + 16 + 63) / 64) * 16384); }
+
+int launch_prepare_pipe(const void* basis, const void* cscale, const void* mean, int nkv, int rank, void* out,
+                        cudaStream_t st) {
+  cudaError_t e = cudaMemsetAsync(out, 0, pipe_wprep_bytes(nkv, rank), st);   // unused tail of the last atom
+  if (e != cudaSuccess) return (int)e;
+  const int total = nkv * HD * (rank + 16);
+  decode_prepare_pipe_kernel<<<(total + 255) / 256, 256, 0, st>>>((const __half*)basis, (const __half*)cscale,
+                                                                   (const __half*)mean, nkv, rank, (unsigned char*)out);
+  return 0;
 }
 
 template <int NW>

@@ -151,6 +151,14 @@ __device__ __forceinline__ uint32_t nib2half2_tc(uint32_t y) {
   const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&biased), __half2half2(__ushort_as_half(0x6408)));
   return *reinterpret_cast<const uint32_t*>(&r);
 }
+// nibbles at bits 4-7 and 20-23 -> half2 of (nibble - 8) without a shift: the masked bits make
+// 1024 + 16*nibble, and one fused multiply-add maps that to nibble - 8 exactly
+__device__ __forceinline__ uint32_t nib2half2_hi(uint32_t y) {
+  const uint32_t biased = (y & 0x00F000F0u) | 0x64006400u;
+  const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&biased), __half2half2(__ushort_as_half(0x2C00)),
+                            __half2half2(__ushort_as_half(0xD480)));   // * 1/16 - 72
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   const __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&h);
