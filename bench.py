@@ -374,7 +374,7 @@ def run_ours(args):
             "decode_tokens_per_s": n_seq_total / (ms_per_step * 1e-3),
             "prefill_compress_s_per_sequence": compress_s, "setup_s": build_s,
             "clean_compress_ratio": ratio,
-            "roofline": {"kernel": "decode_partial_kernel + decode_combine_kernel (one decode_attn call)",
+            "roofline": {"kernel": "decode_partial_pipe_kernel (one decode_attn call: append + split-KV pass + combine)",
                          "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                          "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": None,
                          "us_per_launch": kern_ms * 1e3,
@@ -383,7 +383,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": seqs_per_gpu * L * (N_Q + 2 * N_KV) * HD * 2,
                     "d2h_bytes_per_step": seqs_per_gpu * L * N_Q * HD * 2,
                     "ms_per_step": e2e_ms, "api": "Cache.layers[i].update + fused_attention_compressed"},
-            "gpu_launches": K * (1 + (4 if bd.S > 1 else 3) * L),
+            "gpu_launches": K * (1 + L),
             "clocks": clocks,
         }
         if args.cpu_baseline:
@@ -491,11 +491,11 @@ def run_seqsplit(args):
             "decode_us_per_layer": dec_ms * 1e3 / L, "merge_us_per_layer": mrg_ms * 1e3 / L,
             "merge_overhead_frac": mrg_ms / max(dec_ms + mrg_ms, 1e-9),
             "hbm_gbs_per_gpu": bytes_ls * L / (ms_per_step * 1e-3) / 1e9,
-            "roofline": {"kernel": "decode_partial_pipe_kernel + decode_combine_kernel", "bound": "hbm",
+            "roofline": {"kernel": "decode_partial_pipe_kernel", "bound": "hbm",
                          "achieved": bytes_ls / (dec_ms / L * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
                          "frac": bytes_ls / (dec_ms / L * 1e-3) / 1e9 / hbm_peak, "peak_kind": peak_kind, "traffic": None},
             "e2e": {"value": None, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": K * (1 + L * (4 if first else 3)), "clocks": clocks,
+            "gpu_launches": K * (1 + L * 2), "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -85,7 +85,7 @@ typedef struct ShardDecodeShape {
   int32_t n_stream;       /* streamed tokens to attend to                                */
   int32_t pos_q;          /* position of the query token                                 */
   int32_t partial_out;    /* 0: out = fp16 attention; 1: out = fp32 (m, l, acc) partial  */
-  int32_t reserved;
+  int32_t append;         /* 1: first quantise new_k/new_v into stream row n_stream-1 (fused append) */
 } ShardDecodeShape;
 
 /*
@@ -134,6 +134,12 @@ size_t shard_b200_decode_workspace_bytes(const ShardDecodeShape* shape_host, int
  * bytes, 16-byte aligned; its contents need not be initialised and are overwritten.
  * With shape.partial_out the result is the unnormalised per-head triple
  * (max, sum-exp, acc[128]) in standard V space, ready for shard_b200_lse_merge.
+ * With shape.append the call also does the work of shard_b200_stream_quantize for the newest
+ * token: new_k/new_v are quantised into stream row n_stream-1 (n_stream counts that token)
+ * before the stream is attended to.
+ * The first 16 bytes of the workspace (status word and a ticket counter) must be zero before
+ * the first call that uses a workspace; every call leaves them zero again unless a bounded
+ * wait inside the kernel gave up, in which case the status word is left at 1.
  */
 int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const ShardDecodeShape* shape_host,
                            const float* inv_freq, const float* codebook, void* workspace,

@@ -80,7 +80,14 @@ def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_f
     n_sink = gc["sink_k"].shape[2] if with_fp16_segments else 0
     n_win = gc["win_k"].shape[2] if with_fp16_segments else 0
     n_stream = gc.get("stream_n", 0) if with_fp16_segments else 0
+    pending = gc.pop("_pending", None)
+    if pending is not None and (not with_fp16_segments or pending[2] != n_stream - 1):
+        gc["_pending"] = pending
+        layer._flush_pending()
+        pending = None
     seq = _seq_record(gc, dev)
+    if pending is not None:
+        seq.new_k, seq.new_v = ptr(pending[0]), ptr(pending[1])
     q2 = q_rope.reshape(n_q, hd)
     if not q2.is_contiguous():
         q2 = q2.contiguous()
@@ -90,11 +97,12 @@ def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_f
     seq.q, seq.out = ptr(q2), ptr(out)
     seq.phase = ptr(_phase_for(cache, gc, pos_q, t0, t1, dev)) if t1 > t0 else None
     shape = ops.make_shape(n_q, nkv, gc["k_rank_kernel"], n_comp, t0, t1, n_sink, n_win, n_stream, pos_q,
-                           partial_out)
+                           partial_out, append=pending is not None)
     need = ops.decode_workspace_bytes(shape, 1)
     ws = cache._decode_ws
     if ws is None or ws.numel() < need or ws.device != dev:
-        ws = cache._decode_ws = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+        # zero-filled: the header's status word and arrival counters must start at zero
+        ws = cache._decode_ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dev)
     cb = get_codebook(hd, 8, dev) if n_stream > 0 else None
     ops.decode_attn(seq, 1, shape, cache._inv_freq(dev), cb, ws)
     return out

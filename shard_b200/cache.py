@@ -194,8 +194,9 @@ class CacheLayer(CacheLayerMixin):
 
         if gc is not None and c._streaming:
             for t in range(seq_new):
+                # with the fused decode the last token is quantised inside the decode launch
                 self._stream_append(key_states[:, :, t:t + 1, :], value_states[:, :, t:t + 1, :],
-                                    self._seq_len + t)
+                                    self._seq_len + t, defer=fused and t == seq_new - 1)
             self._seq_len += seq_new
             self._needs_decompress = True
             if fused:
@@ -228,9 +229,20 @@ class CacheLayer(CacheLayerMixin):
         return self._keys, self._values
 
     # -- 8-bit stream -----------------------------------------------------------
-    def _stream_append(self, k, v, position):
+    def _flush_pending(self):
+        """Quantise a token whose append was left to the next decode launch and never got one."""
+        gc = self._gpu_compressed
+        pend = gc.pop("_pending", None) if gc is not None else None
+        if pend is not None:
+            k2, v2, slot = pend
+            ops.stream_quantize(k2, v2, gc["signs"], get_codebook(k2.shape[-1], 8, k2.device),
+                                gc["k_idx_buf"], gc["v_idx_buf"], gc["k_norm_buf"], gc["v_norm_buf"], slot)
+
+    def _stream_append(self, k, v, position, defer=False):
         """Quantise one (1, nkv, 1, hd) token into the stream buffers
-        (reference: src/shard/cache.py:193-241)."""
+        (reference: src/shard/cache.py:193-241).  With `defer` the row is reserved and the
+        token is handed to the next `decode_layer` call, whose kernel quantises it."""
+        self._flush_pending()
         gc = self._gpu_compressed
         c = self._cache_ref
         if c._stream_qjl:
@@ -260,12 +272,17 @@ class CacheLayer(CacheLayerMixin):
         v2 = v.reshape(heads, hd)
         if k2.dtype != torch.float16:
             raise NotImplementedError("fp16 models only")
-        ops.stream_quantize(k2.contiguous(), v2.contiguous(), gc["signs"], get_codebook(hd, 8, dev),
-                            gc["k_idx_buf"], gc["v_idx_buf"], gc["k_norm_buf"], gc["v_norm_buf"], s)
+        if defer:
+            gc["_pending"] = (k2.contiguous(), v2.contiguous(), s)
+        else:
+            ops.stream_quantize(k2.contiguous(), v2.contiguous(), gc["signs"], get_codebook(hd, 8, dev),
+                                gc["k_idx_buf"], gc["v_idx_buf"], gc["k_norm_buf"], gc["v_norm_buf"], s)
         gc["stream_n"] = s + 1
 
     def _dequant_stream(self, gc=None, *unused):
         """fp16 (1, nkv, s, hd) K and V of the streamed tokens (reference: cache.py:243-279)."""
+        if gc is None or gc is self._gpu_compressed:
+            self._flush_pending()
         gc = self._gpu_compressed if gc is None else gc
         s = gc.get("stream_n", 0)
         if s == 0 or "k_idx_buf" not in gc:

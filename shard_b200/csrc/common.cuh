@@ -75,4 +75,36 @@ __device__ __forceinline__ int lloyd_max_code(float v, const float* __restrict__
   return dl < dr ? left : idx;
 }
 
+// 8-bit Lloyd-Max code of one 128-channel fp16 vector, one warp per vector (lane l owns
+// channels 4l..4l+3): exact fp64 norm, IEEE division, butterfly in stage order, nearest
+// codebook entry with ties to the right.  Writes 128 codes and the fp16 norm.
+__device__ __forceinline__ void quantize_vec_warp(const __half* __restrict__ src, const float* __restrict__ signs,
+                                                  const float* __restrict__ cb, uint8_t* __restrict__ idx_out,
+                                                  __half* __restrict__ norm_out, int lane) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(src + 4 * lane);
+  const __half2 h01 = *reinterpret_cast<const __half2*>(&raw.x);
+  const __half2 h23 = *reinterpret_cast<const __half2*>(&raw.y);
+  float x[4] = {__low2float(h01), __high2float(h01), __low2float(h23), __high2float(h23)};
+  double ss = 0.0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) ss += (double)x[i] * (double)x[i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  float n = (float)sqrt(ss);
+  n = fmaxf(n, 1e-8f);
+  const float4 sg = *reinterpret_cast<const float4*>(signs + 4 * lane);
+  const float sgn[4] = {sg.x, sg.y, sg.z, sg.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) x[i] = __fmul_rn(__fdiv_rn(x[i], n), sgn[i]);
+  fwht128_lane4(x, lane);
+  uint32_t packed = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float r = __fdiv_rn(x[i], SQRT_HD);
+    packed |= (uint32_t)lloyd_max_code(r, cb, 256) << (8 * i);
+  }
+  *reinterpret_cast<uint32_t*>(idx_out + 4 * lane) = packed;
+  if (lane == 0) *norm_out = __float2half_rn(n);
+}
+
 }  // namespace shard

@@ -31,7 +31,11 @@ constexpr int TILE_TOK = 16;           // tokens per warp tile of the mma.sync k
 constexpr int MMA_CTA_SLOTS = 148 * 3; // resident CTAs of the mma.sync kernel on a B200
 constexpr int TC_TILE_TOK = 128;       // tokens per tile of the tcgen05 kernel
 constexpr int PIPE_CTA_SLOTS = 148;    // the pipelined kernel keeps one CTA per SM
-constexpr int WS_HEADER_BYTES = 16;    // status word + padding in front of the partial records
+constexpr int WS_STATUS_BYTES = 16;    // status word + padding at the very front of the scratch
+// header = status word, then one arrival counter per (sequence, KV head), rounded to 16 bytes
+static inline size_t ws_header_bytes(int batch, int nkv) {
+  return WS_STATUS_BYTES + (((size_t)batch * nkv * sizeof(int) + 15) & ~(size_t)15);
+}
 
 // implemented in decode_pipe.cu
 size_t pipe_wprep_bytes(int nkv, int rank);
@@ -505,11 +509,11 @@ static int check_shape(const ShardDecodeShape* sh) {
   return SHARD_OK;
 }
 
-// scratch layout: 16-byte header (status word), [batch][n_parts][n_q][132] fp32 partial records,
-// then (batch > 1) `batch` out pointers
+// scratch layout: header (status word, arrival counters; zero between calls),
+// [batch][n_parts][n_q][132] fp32 partial records, then (batch > 1) `batch` out pointers
 static size_t ws_bytes(const ShardDecodeShape& sh, int batch) {
   const DecodePlan pl = make_plan(sh, batch);
-  size_t b = WS_HEADER_BYTES + (size_t)batch * pl.n_parts * sh.n_q * PART * sizeof(float);
+  size_t b = ws_header_bytes(batch, sh.nkv) + (size_t)batch * pl.n_parts * sh.n_q * PART * sizeof(float);
   if (batch > 1) b += (size_t)batch * sizeof(void*);
   return b;
 }
@@ -527,6 +531,7 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
   if (rc != SHARD_OK) return rc;
   const ShardDecodeShape& sh = *shape_host;
   if (sh.n_stream > 0 && !codebook) return SHARD_E_ARG;
+  if (sh.append && (sh.n_stream < 1 || (batch == 1 && (!seqs->new_k || !seqs->new_v)))) return SHARD_E_ARG;
   if ((uintptr_t)workspace & 15) return SHARD_E_ALIGN;
   if (workspace_bytes < ws_bytes(sh, batch)) return SHARD_E_WORKSPACE;
   const DecodePlan pl = make_plan(sh, batch);
@@ -554,11 +559,13 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
   } else {
     p.table = seqs;
   }
+  const size_t header = ws_header_bytes(batch, sh.nkv);
   p.sh = sh;
   p.inv_freq = inv_freq;
   p.codebook = codebook;
-  p.ws = (float*)((unsigned char*)workspace + WS_HEADER_BYTES);
+  p.ws = (float*)((unsigned char*)workspace + header);
   p.status = (int*)workspace;
+  p.tickets = (int*)((unsigned char*)workspace + WS_STATUS_BYTES);
   p.n_chunks = pl.n_chunks;
   p.tiles_per_chunk = pl.tiles_per_chunk;
   p.tiles_rem = pl.tiles_rem;
@@ -568,9 +575,17 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
 
   dim3 grid(pl.n_parts, sh.nkv, batch);
   if (decode_mode() == MODE_PIPE) {
+    // one launch: the append (if asked for), the split-KV pass and the combine
     if (batch == 1 && ((uintptr_t)p.one.k_coeffs & 15)) return SHARD_E_ALIGN;
     rc = launch_partial_pipe(p, grid, st);
+    if (rc) return rc;
+    SHARD_CHECK_LAUNCH();
+    return SHARD_OK;
   } else {
+    if (sh.append) {
+      rc = shard_b200_stream_quantize(seqs, batch, sh.nkv, sh.n_stream - 1, codebook, stream);
+      if (rc) return rc;
+    }
     switch (sh.rank / 32) {
       case 1: rc = launch_partial<1>(p, grid, st); break;
       case 2: rc = launch_partial<2>(p, grid, st); break;
@@ -585,7 +600,7 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
 
   void** out_table = nullptr;
   if (batch > 1) {
-    out_table = reinterpret_cast<void**>(reinterpret_cast<unsigned char*>(workspace) + WS_HEADER_BYTES +
+    out_table = reinterpret_cast<void**>(reinterpret_cast<unsigned char*>(workspace) + header +
                                          (size_t)batch * pl.n_parts * sh.n_q * PART * sizeof(float));
     gather_out_ptrs_kernel<<<(batch + 127) / 128, 128, 0, st>>>(seqs, batch, out_table);
   }
@@ -649,9 +664,10 @@ extern "C" int shard_b200_decode_attn_noalloc(const ShardSeq* seq_host, const Sh
   void* scratch = nullptr;
   rc = static_scratch_for_current_device(&scratch);
   if (rc != SHARD_OK) return rc;
-  // The array still holds whatever the previous call left there.  Only the status word in
-  // the header has to start at zero; every partial record is rewritten before it is read.
-  cudaError_t e = cudaMemsetAsync(scratch, 0, WS_HEADER_BYTES, (cudaStream_t)stream);
+  // The array still holds whatever the previous call left there.  Only the header (status
+  // word and arrival counters) has to start at zero; every partial record is rewritten
+  // before it is read.
+  cudaError_t e = cudaMemsetAsync(scratch, 0, ws_header_bytes(1, shape_host->nkv), (cudaStream_t)stream);
   if (e != cudaSuccess) return (int)e;
   return shard_b200_decode_attn(seq_host, 1, shape_host, inv_freq, codebook, scratch,
                                 (size_t)SHARD_B200_STATIC_SCRATCH_BYTES, stream);

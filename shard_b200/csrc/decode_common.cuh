@@ -17,6 +17,7 @@ struct DecodeParams {
   const float* codebook;
   float* ws;
   int* status;          // device word set non-zero when a bounded wait gave up
+  int* tickets;         // [batch][nkv] arrival counters of the fused combine (zero between calls)
   int n_chunks;         // CTAs (per KV head) that walk the compressed middle
   int tiles_per_chunk;
   int tiles_rem;        // pipelined kernel: the first tiles_rem chunks walk one tile more
@@ -46,7 +47,8 @@ __device__ __forceinline__ void softmax_init(SoftmaxState& st) {
 __device__ __forceinline__ void stream_dequant_lane4(const uint8_t* __restrict__ idx_row, float nrm,
                                                      const float* __restrict__ cbs, const float4 sg, int lane,
                                                      float (&o)[4]) {
-  const uint32_t codes = *reinterpret_cast<const uint32_t*>(idx_row + 4 * lane);
+  // L2-coherent load: the row may have been written by this CTA a moment ago (fused append)
+  const uint32_t codes = __ldcg(reinterpret_cast<const unsigned int*>(idx_row + 4 * lane));
   float x[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) x[i] = cbs[(codes >> (8 * i)) & 0xff];
@@ -95,6 +97,20 @@ __device__ __forceinline__ void stage_query(const ShardSeq& sq, int kv, int pos_
   }
 }
 
+// Fused append: the CTA that owns streamed row n_stream-1 first quantises the step's new
+// K/V vector of its KV head into that row (warp 0: K, warp 1: V).  The caller synchronises
+// the CTA afterwards; the rows are then read back with L2-coherent loads.
+__device__ __forceinline__ void append_new_token(const ShardSeq& sq, const ShardDecodeShape& sh, int kv,
+                                                 const float* __restrict__ cbs, int warp, int lane) {
+  if (warp >= 2) return;
+  const bool is_v = warp == 1;
+  const size_t row = (size_t)(sh.n_stream - 1) * sh.nkv + kv;
+  const __half* src = reinterpret_cast<const __half*>(is_v ? sq.new_v : sq.new_k) + kv * HD;
+  uint8_t* idx_out = (is_v ? sq.st_v_idx : sq.st_k_idx) + row * HD;
+  __half* norm_out = reinterpret_cast<__half*>(is_v ? sq.st_v_norm : sq.st_k_norm) + row;
+  quantize_vec_warp(src, sq.signs, cbs, idx_out, norm_out, lane);
+}
+
 // fp16 rows (sink + window) or streamed rows [u_lo, u_hi): one warp per token, lane owns
 // channels 4*lane..+3.  `qr` is the query as given (fp32 copy in shared memory), `cbs` the
 // stream codebook in shared memory (streamed rows only).
@@ -127,8 +143,8 @@ __device__ __forceinline__ void process_rows(SoftmaxState& st, const ShardSeq& s
       vx[0] = v01.x; vx[1] = v01.y; vx[2] = v23.x; vx[3] = v23.y;
     } else {
       const size_t row = (size_t)u * sh.nkv + kv;
-      const float kn = __half2float(reinterpret_cast<const __half*>(sq.st_k_norm)[row]);
-      const float vn = __half2float(reinterpret_cast<const __half*>(sq.st_v_norm)[row]);
+      const float kn = __half2float(__ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(sq.st_k_norm) + row)));
+      const float vn = __half2float(__ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(sq.st_v_norm) + row)));
       stream_dequant_lane4(sq.st_k_idx + row * HD, kn, cbs, sg, lane, kx);
       stream_dequant_lane4(sq.st_v_idx + row * HD, vn, cbs, sg, lane, vx);
     }
@@ -182,6 +198,73 @@ __device__ __forceinline__ void emit_partial(const SoftmaxState& st, float* __re
       if (d == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
       rec[4 + d] = a;
     }
+  }
+}
+
+// Fused combine.  Every CTA of one (sequence, KV head) calls this after its record is written.
+// Each takes a ticket; the CTA that draws the last one sees all records of that KV head
+// (release/acquire through the fences around the ticket), merges them for the head's four
+// query heads exactly as decode_combine_kernel does (same order, same operations), and puts
+// the counter back to zero for the next call.  `sm` needs GQA*HD floats that are free;
+// NTHREADS >= GQA*HD.  Thread tid handles head tid/128, channel tid%128.
+template <int NTHREADS>
+__device__ __forceinline__ void ticket_combine(const DecodeParams& p, const ShardSeq& sq, int kv, int b,
+                                               float* sm_raw, int tid) {
+  volatile float* sm = sm_raw;   // exchanged between threads: every access must reach shared memory
+  static_assert(NTHREADS >= GQA * HD, "one thread per (head, channel)");
+  __shared__ int last_s;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    int* ctr = p.tickets + b * p.sh.nkv + kv;
+    const int last = atomicAdd(ctr, 1) == p.n_parts - 1;
+    if (last) atomicExch(ctr, 0);
+    last_s = last;
+  }
+  __syncthreads();
+  if (!last_s) return;
+  __threadfence();
+  const bool active = tid < GQA * HD;
+  const int n_q = p.sh.n_q, n_parts = p.n_parts, n_rot = p.n_chunks;
+  const int h = kv * GQA + ((tid >> 7) & (GQA - 1)), d = tid & (HD - 1);
+  const float* base = p.ws + ((size_t)b * n_parts * n_q + h) * PART;
+  const size_t pstride = (size_t)n_q * PART;
+  float M = neg_inf(), L = 0.f, rot = 0.f, stdv = 0.f;
+  if (active) {
+#pragma unroll 8
+    for (int pi = 0; pi < n_parts; ++pi) M = fmaxf(M, __ldcg(base + pi * pstride));
+#pragma unroll 8
+    for (int pi = 0; pi < n_parts; ++pi) {
+      const float* rec = base + pi * pstride;
+      const float m = __ldcg(rec);
+      const float l = __ldcg(rec + 1);
+      const float a = __ldcg(rec + 4 + d);
+      const float wt = (m == neg_inf()) ? 0.f : exp2f((m - M) * LOG2E);
+      L = fmaf(wt, l, L);
+      if (pi < n_rot) rot = fmaf(wt, a, rot); else stdv = fmaf(wt, a, stdv);
+    }
+  }
+  float v = rot;
+  if (n_rot > 0) {
+    for (int hh = 1; hh < HD; hh <<= 1) {
+      if (active) sm[tid] = v;
+      __syncthreads();
+      if (active) {
+        const float other = sm[tid ^ hh];
+        v = (d & hh) ? other - v : v + other;
+      }
+      __syncthreads();
+    }
+    v = v / SQRT_HD;
+  }
+  if (!active) return;
+  const float o = v + stdv;
+  if (p.sh.partial_out) {
+    float* rec = reinterpret_cast<float*>(sq.out) + (size_t)h * PART;
+    if (d == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
+    rec[4 + d] = o;
+  } else {
+    reinterpret_cast<__half*>(sq.out)[(size_t)h * HD + d] = __float2half_rn(o / L);
   }
 }
 

@@ -136,11 +136,16 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       u_lo = (part - p.n_chunks - p.n_fp16_ctas) * STREAM_TOK_PER_CTA;
       u_hi = min(u_lo + STREAM_TOK_PER_CTA, sh.n_stream);
     }
+    if (!is_fp16 && sh.append && u_hi == sh.n_stream) {   // this CTA owns the newest streamed row
+      append_new_token(sq, sh, kv, cbs, warp, lane);
+      __syncthreads();
+    }
     SoftmaxState st;
     softmax_init(st);
     process_rows<PP_WARPS>(st, sq, sh, kv, is_fp16, u_lo, u_hi, qr, cbs, warp, lane);
     __syncthreads();
     emit_partial<PP_WARPS>(st, scratch, rec_base, tid, warp, lane);
+    ticket_combine<PP_THREADS>(p, sq, kv, blockIdx.z, scratch, tid);
     return;
   }
 
@@ -491,6 +496,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   tc_fence_before();
   __syncthreads();
   if (warp == PP_UNPACK_WARP0) tmem_dealloc(tmem_base, PP_TMEM_COLS);
+  ticket_combine<PP_THREADS>(p, sq, kv, blockIdx.z, reinterpret_cast<float*>(w_s), tid);
 #ifdef SHARD_TC_DEBUG
   if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 49] += clock64() - pp_kstart__;
   if (g_pp_debug && tid < 48)

@@ -30,36 +30,10 @@ __global__ void __launch_bounds__(128) stream_quantize_kernel(const __grid_const
   if (vec >= 2 * p.nkv) return;
   const bool is_v = vec >= p.nkv;
   const int kv = is_v ? vec - p.nkv : vec;
-  const __half* src = reinterpret_cast<const __half*>(is_v ? s.new_v : s.new_k) + kv * HD + 4 * lane;
-  uint8_t* idx_out = (is_v ? s.st_v_idx : s.st_k_idx) + ((size_t)p.slot * p.nkv + kv) * HD + 4 * lane;
+  const __half* src = reinterpret_cast<const __half*>(is_v ? s.new_v : s.new_k) + kv * HD;
+  uint8_t* idx_out = (is_v ? s.st_v_idx : s.st_k_idx) + ((size_t)p.slot * p.nkv + kv) * HD;
   __half* norm_out = reinterpret_cast<__half*>(is_v ? s.st_v_norm : s.st_k_norm) + (size_t)p.slot * p.nkv + kv;
-
-  const uint2 raw = *reinterpret_cast<const uint2*>(src);
-  const __half2 h01 = *reinterpret_cast<const __half2*>(&raw.x);
-  const __half2 h23 = *reinterpret_cast<const __half2*>(&raw.y);
-  float x[4] = {__low2float(h01), __high2float(h01), __low2float(h23), __high2float(h23)};
-
-  double ss = 0.0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) ss += (double)x[i] * (double)x[i];
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  float n = (float)sqrt(ss);
-  n = fmaxf(n, 1e-8f);
-
-  const float4 sg = *reinterpret_cast<const float4*>(s.signs + 4 * lane);
-  const float sgn[4] = {sg.x, sg.y, sg.z, sg.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) x[i] = __fmul_rn(__fdiv_rn(x[i], n), sgn[i]);
-  fwht128_lane4(x, lane);
-  uint32_t packed = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float r = __fdiv_rn(x[i], SQRT_HD);
-    packed |= (uint32_t)lloyd_max_code(r, cb, 256) << (8 * i);
-  }
-  *reinterpret_cast<uint32_t*>(idx_out) = packed;
-  if (lane == 0) *norm_out = __float2half_rn(n);
+  quantize_vec_warp(src, s.signs, cb, idx_out, norm_out, lane);
 }
 
 // out[kv][t][:] = fp16( fp32(fp16(H128(cb[idx]) / sqrt(128) * signs)) * fp32(norm) )

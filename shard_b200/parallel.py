@@ -176,27 +176,26 @@ class BatchedDecoder:
                 seqs.append(s)
             self.tables.append(ops.seq_table(seqs, dev) if S > 1 else seqs[0])
         shape = self._shape(0, self.capacity)
-        self.ws = torch.empty(ops.decode_workspace_bytes(shape, S), dtype=torch.uint8, device=dev)
+        self.ws = torch.zeros(ops.decode_workspace_bytes(shape, S), dtype=torch.uint8, device=dev)
 
-    def _shape(self, pos_q, n_stream):
+    def _shape(self, pos_q, n_stream, append=False):
         return ops.make_shape(self.n_q, self.nkv, self.rank_k, self.n_comp, 0, self.n_comp,
-                              self.n_sink, self.n_win, n_stream, pos_q, False)
+                              self.n_sink, self.n_win, n_stream, pos_q, False, append=append)
 
     def step(self, pos_q):
         """Append self.new_k/new_v (all layers, all sequences) to the streams, then attend
-        with self.q; results land in self.out.  Launches 1 + 3 * n_layers kernels."""
+        with self.q; results land in self.out.  Launches 1 + n_layers kernels: the phase table,
+        then per layer one kernel that appends, attends and combines."""
         if self.n_stream >= self.capacity:
             raise _lib.ShardError("stream capacity exhausted")
         lib = _lib.load()
         st = _lib.cur_stream()
         ops.phase_table(self.compress_start, pos_q, self.n_comp, self.inv_freq, out=self.phase)
-        shape = self._shape(pos_q, self.n_stream + 1)
+        shape = self._shape(pos_q, self.n_stream + 1, append=True)
         import ctypes as C
         for li in range(self.n_layers):
             tab = self.tables[li]
             tptr = tab.data_ptr() if self.S > 1 else C.addressof(tab)
-            _lib.check(lib.shard_b200_stream_quantize(tptr, self.S, self.nkv, self.n_stream,
-                                                      ptr(self.codebook), st), "stream_quantize")
             _lib.check(lib.shard_b200_decode_attn(tptr, self.S, C.byref(shape), ptr(self.inv_freq),
                                                   ptr(self.codebook), ptr(self.ws), self.ws.numel(), st),
                        "decode_attn")

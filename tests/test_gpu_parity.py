@@ -277,6 +277,41 @@ def test_decode_stream_only_and_many_stream_tokens(ops, codebook):
     _check_random(48, 192, 0, 0, pos_q=400, n_stream=255, seed=12)
 
 
+def test_decode_fused_append_equals_separate_append(ops, codebook):
+    """shape.append: the decode launch quantises the new token itself.  Stream rows must be
+    bit-identical to the oracle's codes and the attention identical to append-then-decode,
+    at a CTA boundary of the stream (32 rows per CTA) and inside one."""
+    from shard_b200.attention import _seq_record
+    from shard_b200 import _lib
+    cbo = O.lloyd_max_codebook(128, 8)
+    for n_prev in (0, 31, 32, 45):
+        layer, gc_np, q, _ = _check_random(700, 192, 4, 64, pos_q=900, n_stream=max(n_prev, 1), seed=40 + n_prev)
+        gc = layer._gpu_compressed
+        cap = n_prev + 1
+        for key in ("k_idx_buf", "v_idx_buf", "k_norm_buf", "v_norm_buf"):
+            old = gc[key][:n_prev]
+            new = torch.zeros((cap, *old.shape[1:]), dtype=old.dtype, device=DEV)
+            new[:n_prev].copy_(old)
+            gc[key] = new
+        rng = np.random.default_rng(n_prev)
+        nk = rng.standard_normal((8, 128)).astype(np.float16)
+        nv = (3 * rng.standard_normal((8, 128))).astype(np.float16)
+        signs = N(gc["signs"])
+        ki, kn, vi, vn = O.stream_quantize(nk[None], nv[None], signs, cbo)
+        # fused: pending token consumed by decode_layer
+        gc["_pending"] = (T(nk), T(nv), n_prev)
+        gc["stream_n"] = n_prev + 1
+        fused = _decode(layer, q, 900)
+        assert "_pending" not in gc
+        assert np.array_equal(N(gc["k_idx_buf"][n_prev, 0]), ki[0])
+        assert np.array_equal(N(gc["v_idx_buf"][n_prev, 0]), vi[0])
+        assert np.array_equal(N(gc["k_norm_buf"][n_prev, 0]), kn[0])
+        assert np.array_equal(N(gc["v_norm_buf"][n_prev, 0]), vn[0])
+        # separate: rows already in place, plain decode
+        sep = _decode(layer, q, 900)
+        assert np.array_equal(fused, sep)
+
+
 def test_decode_token_ranges_merge_to_whole(ops):
     """Sequence-split on one GPU: partials of disjoint token ranges + lse_merge == whole."""
     layer, gc_np, q, whole = _check_random(3000, 192, 4, 64, pos_q=3200, seed=21)
