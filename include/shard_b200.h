@@ -51,7 +51,7 @@ const char* shard_b200_status_string(int status);
  * CacheLayer._stream_append (src/shard/cache.py:193-241).
  */
 typedef struct ShardSeq {
-  const uint8_t* k_coeffs;   /* [n_comp][rank/2]  packed int4 PCA coefficients          */
+  const uint8_t* k_coeffs;   /* [n_comp][rank/2]  packed int4 PCA coefficients, 16-byte aligned */
   const void* k_wprep;       /* output of shard_b200_decode_prepare for this layer      */
   const uint8_t* v_indices;  /* [nkv][n_comp][32] VQ codes                              */
   const void* v_centroids;   /* fp16 [256][4]                                           */
@@ -65,7 +65,7 @@ typedef struct ShardSeq {
   void* st_k_norm;           /* fp16 [cap][nkv]                                         */
   void* st_v_norm;           /* fp16 [cap][nkv]                                         */
   const float* signs;        /* [128] +-1, per layer                                    */
-  const void* phase;         /* fp16x2 [n_comp][64] (cos, sin) from shard_b200_phase_table */
+  const void* phase;         /* table written by shard_b200_phase_table for [tok_begin, tok_end) */
   const void* q;             /* fp16 [n_q][128]   query, RoPE applied at pos_q          */
   void* out;                 /* fp16 [n_q][128] result, or fp32 [n_q][132] partial      */
   const void* new_k;         /* fp16 [nkv][128]   token to append (stream_quantize)     */
@@ -90,11 +90,15 @@ typedef struct ShardDecodeShape {
 
 /*
  * cos/sin of fp32(compress_start + t - pos_q) * inv_freq[i], rounded to fp16, for
- * t in [0, n_comp), i in [0, 64): the table of src/shard/attention.py:76-79.
+ * t in [0, n_tok), i in [0, 64): the table of src/shard/attention.py:76-79.
  * It depends only on positions, so one table serves every layer of a step.
- * out: fp16x2 [n_comp][64], (cos, sin) interleaved.
+ * out (16-byte aligned, shard_b200_phase_table_bytes(n_tok) bytes) is opaque to the caller:
+ * tokens are grouped in blocks of 32, and a block stores 16 planes of 32 x 16 bytes -- plane c < 8
+ * the cosines of pairs 8c..8c+7 for each of its tokens, plane 8 + c the sines -- so that a warp
+ * owning 32 consecutive tokens reads each plane as one contiguous 512-byte run.
  */
-int shard_b200_phase_table(int32_t compress_start, int32_t pos_q, int32_t n_comp,
+size_t shard_b200_phase_table_bytes(int32_t n_tok);
+int shard_b200_phase_table(int32_t compress_start, int32_t pos_q, int32_t n_tok,
                            const float* inv_freq, void* out, void* stream);
 
 /*

@@ -35,6 +35,7 @@ class ShardDecodeShape(C.Structure):
 _SIGNATURES = {
     "shard_b200_abi_version": (C.c_int, []),
     "shard_b200_status_string": (C.c_char_p, [C.c_int]),
+    "shard_b200_phase_table_bytes": (C.c_size_t, [C.c_int32]),
     "shard_b200_phase_table": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
     "shard_b200_wprep_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
     "shard_b200_decode_prepare": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,

@@ -24,8 +24,8 @@ def _phase_for(cache, gc, pos_q, tok_begin, tok_end, dev):
     key = (int(pos_q), gc["compress_start"], tok_begin, tok_end)
     if cache._phase_key != key:
         n = tok_end - tok_begin
-        if cache._phase is None or cache._phase.shape[0] < n:
-            cache._phase = torch.empty(max(n, 1), 64, 2, dtype=torch.float16, device=dev)
+        if cache._phase is None or cache._phase.numel() < ops.phase_table_numel(n):
+            cache._phase = torch.empty(ops.phase_table_numel(n), dtype=torch.float16, device=dev)
         ops.phase_table(gc["compress_start"] + tok_begin, pos_q, n, cache._inv_freq(dev), out=cache._phase)
         cache._phase_key = key
     return cache._phase

@@ -1,23 +1,17 @@
-// Fused decode attention over a compressed KV cache (one query token).
+// Fused decode attention over a compressed KV cache (one query token): host side of the
+// C ABI, the phase-table kernel and the stand-alone log-sum-exp merge.
 //
 //   score(h, t) = q_h . RoPE_{pos_t}( W coef_t + mean )        compressed middle
 //   score(h, t) = q_h . k_t                                     fp16 sink / window / stream
 //   out_h       = softmax_t(score / sqrt(128)) . V_t
 //
-// Kernels in this file
-//   phase_table_kernel    cos/sin(fp32(pos_t - pos_q) * inv_freq) in fp16, shared by all layers
-//   decode_prepare_kernel folds the coefficient scale into the PCA basis, appends the
-//                         mean as one more contraction column and stores the result in
-//                         mma fragment order
-//   decode_partial_kernel split-KV pass: every CTA attends to a chunk of tokens for one
-//                         KV head (4 query heads) and emits (max, sum-exp, acc[128])
-//   decode_combine_kernel log-sum-exp combine of the partials, one inverse Hadamard on
-//                         the summed rotated-space part, final normalisation
-//
-// The middle segment never materialises K: a warp reconstructs the un-rotated keys of
-// 16 tokens for one KV head as a [16 x R] x [R x 128] tensor-core product straight from
-// the packed int4 coefficients (nibbles are expanded to fp16 in registers), rotates
-// them by the relative phase, and dots them with the un-rotated query.
+// Kernels
+//   phase_table_kernel          cos/sin(fp32(pos_t - pos_q) * inv_freq) in fp16, shared by all layers
+//   decode_partial_pipe_kernel  (decode_pipe.cu) one launch per layer-step: optional stream append,
+//                               split-KV pass over the middle / fp16 rows / streamed rows, and the
+//                               combine, done by the last CTA of each KV head to arrive
+//   decode_combine_kernel       the same combine as a kernel of its own, for merging the partial
+//                               records of several launches or several GPUs (shard_b200_lse_merge)
 #include <cstdlib>
 #include <mutex>
 
@@ -25,12 +19,8 @@
 
 namespace shard {
 
-constexpr int DEC_THREADS = 128;
-constexpr int DEC_WARPS = 4;
-constexpr int TILE_TOK = 16;           // tokens per warp tile of the mma.sync kernel
-constexpr int MMA_CTA_SLOTS = 148 * 3; // resident CTAs of the mma.sync kernel on a B200
-constexpr int TC_TILE_TOK = 128;       // tokens per tile of the tcgen05 kernel
-constexpr int PIPE_CTA_SLOTS = 148;    // the pipelined kernel keeps one CTA per SM
+constexpr int TILE_TOK = 128;          // tokens per tile of the middle segment
+constexpr int CTA_SLOTS = 148;         // the decode kernel keeps one CTA per SM of a B200
 constexpr int WS_STATUS_BYTES = 16;    // status word + padding at the very front of the scratch
 // header = status word, then one arrival counter per (sequence, KV head), rounded to 16 bytes
 static inline size_t ws_header_bytes(int batch, int nkv) {
@@ -43,52 +33,23 @@ int launch_prepare_pipe(const void* basis, const void* cscale, const void* mean,
                         cudaStream_t st);
 int launch_partial_pipe(const DecodeParams& p, dim3 grid, cudaStream_t st);
 
-__host__ __device__ inline size_t pipe_blob_bytes(int nkv, int rank) {
-  return (size_t)nkv * (((rank + 16 + 63) / 64) * 16384);
-}
-
 struct DecodePlan {
   int n_chunks, tiles_per_chunk, tiles_rem, n_fp16_ctas, n_stream_ctas, n_parts;
 };
 
-// Which kernel walks the compressed middle: the pipelined tcgen05 kernel (default), or the
-// earlier mma.sync kernel kept for A/B timing (environment SHARD_B200_DECODE=mma).
-enum DecodeMode { MODE_PIPE = 0, MODE_MMA = 2 };
-static DecodeMode decode_mode() {
-  static int mode = -1;
-  if (mode < 0) {
-    const char* e = getenv("SHARD_B200_DECODE");
-    mode = (e && e[0] == 'm') ? MODE_MMA : MODE_PIPE;
-  }
-  return (DecodeMode)mode;
-}
-
 static DecodePlan make_plan(const ShardDecodeShape& sh, int batch) {
   DecodePlan pl{};
-  const DecodeMode mode = decode_mode();
-  const int tile_tok = (mode == MODE_MMA) ? TILE_TOK : TC_TILE_TOK;
   const int n_tok = sh.tok_end - sh.tok_begin;
-  const int n_tiles = (n_tok + tile_tok - 1) / tile_tok;
+  const int n_tiles = (n_tok + TILE_TOK - 1) / TILE_TOK;
   const int groups = sh.nkv * batch;
-  if (n_tiles > 0 && mode == MODE_PIPE) {
+  if (n_tiles > 0) {
     // one CTA per SM: spread the tiles of every (sequence, KV head) evenly over its CTAs
-    int chunks = (groups >= PIPE_CTA_SLOTS) ? (n_tiles + 15) / 16 : PIPE_CTA_SLOTS / groups;
+    int chunks = (groups >= CTA_SLOTS) ? (n_tiles + 15) / 16 : CTA_SLOTS / groups;
     if (chunks > n_tiles) chunks = n_tiles;
     if (chunks < 1) chunks = 1;
     pl.n_chunks = chunks;
     pl.tiles_per_chunk = n_tiles / chunks;
     pl.tiles_rem = n_tiles % chunks;
-  } else if (n_tiles > 0) {
-    int tpc;
-    if (groups >= MMA_CTA_SLOTS / 2) {
-      tpc = 64;
-    } else {
-      const int chunks = MMA_CTA_SLOTS / groups;
-      tpc = (n_tiles + chunks - 1) / chunks;
-      if (tpc < DEC_WARPS) tpc = DEC_WARPS;
-    }
-    pl.tiles_per_chunk = tpc;
-    pl.n_chunks = (n_tiles + tpc - 1) / tpc;
   }
   pl.n_fp16_ctas = (sh.n_sink + sh.n_win) > 0 ? 1 : 0;
   pl.n_stream_ctas = (sh.n_stream + STREAM_TOK_PER_CTA - 1) / STREAM_TOK_PER_CTA;
@@ -99,297 +60,30 @@ static DecodePlan make_plan(const ShardDecodeShape& sh, int batch) {
 // ---------------------------------------------------------------------------
 // phase table
 // ---------------------------------------------------------------------------
-// row t of the table: 64 fp16 cosines (pairs 0..63) followed by 64 fp16 sines
+// Layout: tokens in blocks of 32; within a block 16 planes of 32 x 16 bytes: plane c < 8 holds
+// the cosines of pairs 8c..8c+7 of the block's 32 tokens (one 16-byte group per token), plane
+// 8 + c the sines.  A warp whose lanes own 32 consecutive tokens reads a plane as 512
+// contiguous bytes.  One thread computes one token's 8 pairs of one plane pair.
 __global__ void __launch_bounds__(256) phase_table_kernel(int delta0, int n, const float* __restrict__ inv_freq,
-                                                          __half* __restrict__ out) {
-  const size_t total = (size_t)n * HD2;
-  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += (size_t)gridDim.x * blockDim.x) {
-    const int t = (int)(idx >> 6), i = (int)(idx & 63);
-    const float phase = __fmul_rn((float)(delta0 + t), inv_freq[i]);
-    float sn, cs;
-    sincosf(phase, &sn, &cs);
-    out[(size_t)t * HD + i] = __float2half_rn(cs);
-    out[(size_t)t * HD + HD2 + i] = __float2half_rn(sn);
-  }
-}
-
-// ---------------------------------------------------------------------------
-// prepared weights, fragment order: wprep[kv][ks][nt][lane] = (b0, b1)
-//
-// Contraction slots are permuted so that a lane can build its A fragments from
-// one contiguous R/8-byte piece of the packed coefficient row: lane quad index
-// qd owns ranks [R/4*qd, R/4*(qd+1)); 32-bit word w of that piece feeds k-steps
-// 2w and 2w+1.  For k-step ks = 2w+s the fragment slots map to
-//   slot 2qd   -> r = R/4*qd + 8w + 2s        slot 2qd+1 -> r + 4
-//   slot 2qd+8 -> r + 1                       slot 2qd+9 -> r + 5
-// The last k-step carries the mean: slot 0 holds mean[row], A supplies 1.0 there.
-// ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) decode_prepare_kernel(const __half* __restrict__ basis,
-                                                             const __half* __restrict__ cscale,
-                                                             const __half* __restrict__ mean, int nkv, int rank,
-                                                             uint2* __restrict__ out) {
-  const int KD = rank / 16, KS = KD + 1;
-  const int total = nkv * KS * 16 * 32;
-  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= total) return;
-  const int lane = idx & 31;
-  const int nt = (idx >> 5) & 15;
-  const int ks = (idx >> 9) % KS;
-  const int kv = (idx >> 9) / KS;
-  const int g = lane >> 2, qd = lane & 3;
-  const int row = kv * HD + nt * 8 + g;
-  __half v[4];
-  if (ks < KD) {
-    const int w = ks >> 1, s = ks & 1;
-    const int r = (rank / 4) * qd + 8 * w + 2 * s;
-    const int rr[4] = {r, r + 4, r + 1, r + 5};
+                                                          uint4* __restrict__ out) {
+  const int n_blocks = (n + 31) >> 5;
+  const int total = n_blocks * 8 * 32;
+  for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+    const int r = idx & 31, c = (idx >> 5) & 7, blk = idx >> 8;
+    const int t = blk * 32 + r;
+    if (t >= n) continue;
+    uint32_t cw[4], sw[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = __hmul(basis[(size_t)row * rank + rr[i]], cscale[rr[i]]);
-  } else {
-    v[0] = (qd == 0) ? mean[row] : __float2half(0.f);
-    v[1] = v[2] = v[3] = __float2half(0.f);
-  }
-  uint2 o;
-  o.x = (uint32_t)__half_as_ushort(v[0]) | ((uint32_t)__half_as_ushort(v[1]) << 16);
-  o.y = (uint32_t)__half_as_ushort(v[2]) | ((uint32_t)__half_as_ushort(v[3]) << 16);
-  out[idx] = o;
-}
-
-// ---------------------------------------------------------------------------
-// device helpers
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// two nibbles (bits 0-3 and 16-19 of y) -> half2 of (nibble - 8)
-__device__ __forceinline__ uint32_t nib2half2(uint32_t y) {
-  const uint32_t biased = (y & 0x000F000Fu) | 0x64006400u;  // 1024 + nibble
-  const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&biased), __half2half2(__ushort_as_half(0x6408)));
-  return *reinterpret_cast<const uint32_t*>(&r);
-}
-
-// ---------------------------------------------------------------------------
-// split-KV pass
-// ---------------------------------------------------------------------------
-template <int NW>  // 32-bit words of packed coefficients per lane and row = rank / 32
-__global__ void __launch_bounds__(DEC_THREADS, 3) decode_partial_kernel(const __grid_constant__ DecodeParams p) {
-  constexpr int R = NW * 32;
-  constexpr int KD = R / 16;
-  constexpr int W_BYTES = (KD + 1) * 16 * 32 * 8;
-
-  extern __shared__ __align__(16) unsigned char smem[];
-  uint2* wfrag = reinterpret_cast<uint2*>(smem);                          // W_BYTES (aliased later)
-  float* qn = reinterpret_cast<float*>(smem + W_BYTES);                   // [4][128] un-rotated query
-  float* qr = qn + GQA * HD;                                              // [4][128] query as given
-  uint2* cbv = reinterpret_cast<uint2*>(qr + GQA * HD);                   // [256] V codebook (4 x fp16)
-  float* cbs = reinterpret_cast<float*>(cbv + 256);                       // [256] stream codebook
-  float4* p_s = reinterpret_cast<float4*>(cbs + 256);                     // [4 warps][16 tokens]
-  uint8_t* codes_s = reinterpret_cast<uint8_t*>(p_s + DEC_WARPS * TILE_TOK);  // [4 warps][512]
-
-  const ShardSeq& sq = p.table ? p.table[blockIdx.z] : p.one;
-  const ShardDecodeShape& sh = p.sh;
-  const int kv = blockIdx.y;
-  const int part = blockIdx.x;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool is_mid = part < p.n_chunks;
-  const bool is_fp16 = !is_mid && part < p.n_chunks + p.n_fp16_ctas;
-
-  // ---- stage per-CTA constants -------------------------------------------
-  if (is_mid) {
-    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(sq.k_wprep) +
-                                                      pipe_blob_bytes(sh.nkv, R) + (size_t)kv * W_BYTES);
-    uint4* dst = reinterpret_cast<uint4*>(smem);
-    for (int i = tid; i < W_BYTES / 16; i += DEC_THREADS) dst[i] = src[i];
-    const uint2* cb_src = reinterpret_cast<const uint2*>(sq.v_centroids);
-    for (int i = tid; i < 256; i += DEC_THREADS) cbv[i] = cb_src[i];
-  } else if (!is_fp16) {
-    for (int i = tid; i < 256; i += DEC_THREADS) cbs[i] = p.codebook[i];
-  }
-  stage_query(sq, kv, sh.pos_q, p.inv_freq, tid, qn, qr);
-  __syncthreads();
-
-  SoftmaxState st;
-  softmax_init(st);
-
-  if (is_mid) {
-    // ---- compressed middle: 16-token tiles, tensor-core K reconstruction -----
-    const int g = lane >> 2, qd = lane & 3;
-    const int n_tok = sh.tok_end - sh.tok_begin;
-    const int n_tiles = (n_tok + TILE_TOK - 1) / TILE_TOK;
-    const int tile_lo = part * p.tiles_per_chunk;
-    const int tile_hi = min(tile_lo + p.tiles_per_chunk, n_tiles);
-    const __half2* phase_tab = reinterpret_cast<const __half2*>(sq.phase);
-    const uint8_t* vidx = sq.v_indices + (size_t)kv * sh.n_comp * VQ_GROUPS;
-    float4* my_p = p_s + warp * TILE_TOK;
-    uint8_t* my_codes = codes_s + warp * (TILE_TOK * VQ_GROUPS);
-
-    for (int tile = tile_lo + warp; tile < tile_hi; tile += DEC_WARPS) {
-      const int t0 = sh.tok_begin + tile * TILE_TOK;
-      const int tA = t0 + g, tB = t0 + g + 8;
-      const bool okA = tA < sh.tok_end, okB = tB < sh.tok_end;
-      const int tAc = okA ? tA : sh.tok_end - 1, tBc = okB ? tB : sh.tok_end - 1;
-
-      // V codes of the tile -> shared (16 tokens x 32 bytes, one 16-byte piece per lane)
-      {
-        const int tv = min(t0 + (lane >> 1), sh.tok_end - 1);
-        const uint4 c = *reinterpret_cast<const uint4*>(vidx + (size_t)tv * VQ_GROUPS + 16 * (lane & 1));
-        __syncwarp();
-        *reinterpret_cast<uint4*>(my_codes + lane * 16) = c;
-      }
-
-      // packed coefficients of this lane's two rows
-      uint32_t xa[NW], xb[NW];
-      {
-        const uint32_t* ra = reinterpret_cast<const uint32_t*>(sq.k_coeffs + (size_t)tAc * (R / 2) + (R / 8) * qd);
-        const uint32_t* rb = reinterpret_cast<const uint32_t*>(sq.k_coeffs + (size_t)tBc * (R / 2) + (R / 8) * qd);
-#pragma unroll
-        for (int w = 0; w < NW; ++w) { xa[w] = ra[w]; xb[w] = rb[w]; }
-      }
-
-      float acc[16][4];
-#pragma unroll
-      for (int nt = 0; nt < 16; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
-
-#pragma unroll
-      for (int w = 0; w < NW; ++w) {
-#pragma unroll
-        for (int s2 = 0; s2 < 2; ++s2) {
-          const int ks = 2 * w + s2;
-          const uint32_t a0 = nib2half2(xa[w] >> (8 * s2)), a2 = nib2half2(xa[w] >> (8 * s2 + 4));
-          const uint32_t a1 = nib2half2(xb[w] >> (8 * s2)), a3 = nib2half2(xb[w] >> (8 * s2 + 4));
-          const uint2* wf = wfrag + ks * 512 + lane;
-#pragma unroll
-          for (int nt = 0; nt < 16; ++nt) {
-            const uint2 b = wf[nt * 32];
-            mma16816(acc[nt], a0, a1, a2, a3, b.x, b.y);
-          }
-        }
-      }
-      {  // mean column: A = 1.0 in slot 0
-        const uint32_t one = (qd == 0) ? 0x00003C00u : 0u;
-        const uint2* wf = wfrag + KD * 512 + lane;
-#pragma unroll
-        for (int nt = 0; nt < 16; ++nt) {
-          const uint2 b = wf[nt * 32];
-          mma16816(acc[nt], one, one, 0u, 0u, b.x, b.y);
-        }
-      }
-
-      // rotate by the relative phase and dot with the un-rotated query
-      float sA[GQA] = {0.f, 0.f, 0.f, 0.f}, sB[GQA] = {0.f, 0.f, 0.f, 0.f};
-      const __half2* phA = phase_tab + (size_t)(tAc - sh.tok_begin) * HD2 + qd;   // cos pairs; sines 32 further
-      const __half2* phB = phase_tab + (size_t)(tBc - sh.tok_begin) * HD2 + qd;
-#pragma unroll
-      for (int ntp = 0; ntp < 8; ++ntp) {
-        const float2 cosA = __half22float2(phA[4 * ntp]), sinA = __half22float2(phA[32 + 4 * ntp]);
-        const float2 cosB = __half22float2(phB[4 * ntp]), sinB = __half22float2(phB[32 + 4 * ntp]);
-        float2 qa[GQA], qb[GQA];
-#pragma unroll
-        for (int h = 0; h < GQA; ++h) {
-          qa[h] = *reinterpret_cast<const float2*>(qn + h * HD + 8 * ntp + 2 * qd);
-          qb[h] = *reinterpret_cast<const float2*>(qn + h * HD + 64 + 8 * ntp + 2 * qd);
-        }
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float2 csA = e ? make_float2(cosA.y, sinA.y) : make_float2(cosA.x, sinA.x);
-          const float2 csB = e ? make_float2(cosB.y, sinB.y) : make_float2(cosB.x, sinB.x);
-          const float cA = acc[ntp][e], dA = acc[ntp + 8][e];
-          const float cB = acc[ntp][2 + e], dB = acc[ntp + 8][2 + e];
-          const float crA = cA * csA.x - dA * csA.y, drA = dA * csA.x + cA * csA.y;
-          const float crB = cB * csB.x - dB * csB.y, drB = dB * csB.x + cB * csB.y;
-#pragma unroll
-          for (int h = 0; h < GQA; ++h) {
-            const float a = e ? qa[h].y : qa[h].x, b = e ? qb[h].y : qb[h].x;
-            sA[h] = fmaf(a, crA, fmaf(b, drA, sA[h]));
-            sB[h] = fmaf(a, crB, fmaf(b, drB, sB[h]));
-          }
-        }
-      }
-#pragma unroll
-      for (int h = 0; h < GQA; ++h) {
-        sA[h] += __shfl_xor_sync(0xffffffffu, sA[h], 1);
-        sB[h] += __shfl_xor_sync(0xffffffffu, sB[h], 1);
-        sA[h] += __shfl_xor_sync(0xffffffffu, sA[h], 2);
-        sB[h] += __shfl_xor_sync(0xffffffffu, sB[h], 2);
-        sA[h] = okA ? sA[h] * INV_SQRT_HD : neg_inf();
-        sB[h] = okB ? sB[h] * INV_SQRT_HD : neg_inf();
-      }
-
-      // online softmax over the tile
-      float pA[GQA], pB[GQA], alpha[GQA];
-#pragma unroll
-      for (int h = 0; h < GQA; ++h) {
-        float tm = fmaxf(sA[h], sB[h]);
-        tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 4));
-        tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 8));
-        tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 16));
-        const float mn = fmaxf(st.m[h], tm);  // finite: every tile has at least one valid token
-        alpha[h] = (st.m[h] == neg_inf()) ? 0.f : exp2f((st.m[h] - mn) * LOG2E);
-        pA[h] = okA ? exp2f((sA[h] - mn) * LOG2E) : 0.f;
-        pB[h] = okB ? exp2f((sB[h] - mn) * LOG2E) : 0.f;
-        st.m[h] = mn;
-        st.l[h] = st.l[h] * alpha[h] + pA[h] + pB[h];  // lane-local; reduced over g at the end
-#pragma unroll
-        for (int c = 0; c < 4; ++c) st.acc[h][c] *= alpha[h];
-      }
-      if (qd == 0) {
-        my_p[g] = make_float4(pA[0], pA[1], pA[2], pA[3]);
-        my_p[g + 8] = make_float4(pB[0], pB[1], pB[2], pB[3]);
-      }
-      __syncwarp();
-
-      // P.V in the rotated domain: lane owns VQ group `lane` (channels 4*lane..+3)
-#pragma unroll 4
-      for (int tt = 0; tt < TILE_TOK; ++tt) {
-        const float4 pw = my_p[tt];
-        const uint2 ent = cbv[my_codes[tt * VQ_GROUPS + lane]];
-        const float2 v01 = __half22float2(*reinterpret_cast<const __half2*>(&ent.x));
-        const float2 v23 = __half22float2(*reinterpret_cast<const __half2*>(&ent.y));
-        const float pv[GQA] = {pw.x, pw.y, pw.z, pw.w};
-#pragma unroll
-        for (int h = 0; h < GQA; ++h) {
-          st.acc[h][0] = fmaf(pv[h], v01.x, st.acc[h][0]);
-          st.acc[h][1] = fmaf(pv[h], v01.y, st.acc[h][1]);
-          st.acc[h][2] = fmaf(pv[h], v23.x, st.acc[h][2]);
-          st.acc[h][3] = fmaf(pv[h], v23.y, st.acc[h][3]);
-        }
-      }
-      __syncwarp();
+    for (int j = 0; j < 4; ++j) {
+      float sn0, cs0, sn1, cs1;
+      sincosf(__fmul_rn((float)(delta0 + t), inv_freq[8 * c + 2 * j]), &sn0, &cs0);
+      sincosf(__fmul_rn((float)(delta0 + t), inv_freq[8 * c + 2 * j + 1]), &sn1, &cs1);
+      cw[j] = (uint32_t)__half_as_ushort(__float2half_rn(cs0)) | ((uint32_t)__half_as_ushort(__float2half_rn(cs1)) << 16);
+      sw[j] = (uint32_t)__half_as_ushort(__float2half_rn(sn0)) | ((uint32_t)__half_as_ushort(__float2half_rn(sn1)) << 16);
     }
-    // lane-local l -> warp total (quad lanes hold identical copies: reduce over g only)
-#pragma unroll
-    for (int h = 0; h < GQA; ++h) {
-      st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 4);
-      st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 8);
-      st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 16);
-    }
-    // per-channel scale of the rotated V
-    const uint2 chraw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(sq.v_ch) + kv * HD + 4 * lane);
-    const float2 ch01 = __half22float2(*reinterpret_cast<const __half2*>(&chraw.x));
-    const float2 ch23 = __half22float2(*reinterpret_cast<const __half2*>(&chraw.y));
-#pragma unroll
-    for (int h = 0; h < GQA; ++h) {
-      st.acc[h][0] *= ch01.x; st.acc[h][1] *= ch01.y; st.acc[h][2] *= ch23.x; st.acc[h][3] *= ch23.y;
-    }
-  } else {
-    int u_lo = 0, u_hi = sh.n_sink + sh.n_win;
-    if (!is_fp16) {
-      u_lo = (part - p.n_chunks - p.n_fp16_ctas) * STREAM_TOK_PER_CTA;
-      u_hi = min(u_lo + STREAM_TOK_PER_CTA, sh.n_stream);
-    }
-    process_rows<DEC_WARPS>(st, sq, sh, kv, is_fp16, u_lo, u_hi, qr, cbs, warp, lane);
+    out[((size_t)blk * 16 + c) * 32 + r] = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+    out[((size_t)blk * 16 + 8 + c) * 32 + r] = make_uint4(sw[0], sw[1], sw[2], sw[3]);
   }
-
-  // ---- merge the 4 warps and emit this CTA's partial -------------------------
-  __syncthreads();  // all reads of the W fragments are done; reuse that space
-  float* rec_base = p.ws + (((size_t)blockIdx.z * p.n_parts + part) * sh.n_q + (size_t)kv * GQA) * PART;
-  emit_partial<DEC_WARPS>(st, reinterpret_cast<float*>(smem), rec_base, tid, warp, lane);
 }
 
 // ---------------------------------------------------------------------------
@@ -437,50 +131,30 @@ __global__ void __launch_bounds__(HD) decode_combine_kernel(const float* __restr
   }
 }
 
-// tiny helper for batched launches: gather the out pointers of a device ShardSeq table
-__global__ void gather_out_ptrs_kernel(const ShardSeq* table, int batch, void** out) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < batch) out[i] = table[i].out;
-}
-
-template <int NW>
-static int launch_partial(const DecodeParams& p, dim3 grid, cudaStream_t st) {
-  constexpr int W_BYTES = (NW * 2 + 1) * 16 * 32 * 8;
-  constexpr int SMEM = W_BYTES + 2 * GQA * HD * 4 + 256 * 8 + 256 * 4 + DEC_WARPS * TILE_TOK * 16 +
-                       DEC_WARPS * TILE_TOK * VQ_GROUPS;
-  static_assert(SMEM >= (2 * DEC_WARPS * GQA + DEC_WARPS * GQA * HD) * 4, "merge area must fit");
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_partial_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
-  decode_partial_kernel<NW><<<grid, DEC_THREADS, SMEM, st>>>(p);
-  return 0;
-}
-
 }  // namespace shard
 
 using namespace shard;
 
-extern "C" int shard_b200_phase_table(int32_t compress_start, int32_t pos_q, int32_t n_comp, const float* inv_freq,
+extern "C" size_t shard_b200_phase_table_bytes(int32_t n_tok) {
+  if (n_tok < 0) return 0;
+  return (size_t)((n_tok + 31) / 32) * 32 * HD * sizeof(__half);
+}
+
+extern "C" int shard_b200_phase_table(int32_t compress_start, int32_t pos_q, int32_t n_tok, const float* inv_freq,
                                       void* out, void* stream) {
-  if (!inv_freq || !out || n_comp < 0) return SHARD_E_ARG;
-  if (n_comp == 0) return SHARD_OK;
-  const size_t total = (size_t)n_comp * HD2;
-  const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-  phase_table_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(compress_start - pos_q, n_comp, inv_freq,
-                                                                (__half*)out);
+  if (!inv_freq || !out || n_tok < 0) return SHARD_E_ARG;
+  if ((uintptr_t)out & 15) return SHARD_E_ALIGN;
+  if (n_tok == 0) return SHARD_OK;
+  const int total = ((n_tok + 31) / 32) * 256;
+  const int blocks = (total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8;
+  phase_table_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(compress_start - pos_q, n_tok, inv_freq, (uint4*)out);
   SHARD_CHECK_LAUNCH();
   return SHARD_OK;
 }
 
-// blob = [tcgen05 operand layout: nkv x W atoms (mean folded in)] [mma.sync fragment layout]
-static size_t mma_wprep_bytes(int nkv, int rank) { return (size_t)nkv * (rank / 16 + 1) * 16 * 32 * 8; }
-
 extern "C" size_t shard_b200_wprep_bytes(int32_t nkv, int32_t rank) {
   if (nkv < 1 || rank < 32 || rank > 192 || (rank % 32)) return 0;
-  return pipe_wprep_bytes(nkv, rank) + mma_wprep_bytes(nkv, rank);
+  return pipe_wprep_bytes(nkv, rank);
 }
 
 extern "C" int shard_b200_decode_prepare(const void* basis_f16, const void* coeff_scale, const void* mean_f16,
@@ -490,10 +164,6 @@ extern "C" int shard_b200_decode_prepare(const void* basis_f16, const void* coef
   if ((uintptr_t)wprep_out & 15) return SHARD_E_ALIGN;
   int prc = launch_prepare_pipe(basis_f16, coeff_scale, mean_f16, nkv, rank, wprep_out, (cudaStream_t)stream);
   if (prc) return prc;
-  const int total = nkv * (rank / 16 + 1) * 16 * 32;
-  decode_prepare_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
-      (const __half*)basis_f16, (const __half*)coeff_scale, (const __half*)mean_f16, nkv, rank,
-      (uint2*)((unsigned char*)wprep_out + pipe_wprep_bytes(nkv, rank)));
   SHARD_CHECK_LAUNCH();
   return SHARD_OK;
 }
@@ -509,13 +179,11 @@ static int check_shape(const ShardDecodeShape* sh) {
   return SHARD_OK;
 }
 
-// scratch layout: header (status word, arrival counters; zero between calls),
-// [batch][n_parts][n_q][132] fp32 partial records, then (batch > 1) `batch` out pointers
+// scratch layout: header (status word, arrival counters; zero between calls), then
+// [batch][n_parts][n_q][132] fp32 partial records
 static size_t ws_bytes(const ShardDecodeShape& sh, int batch) {
   const DecodePlan pl = make_plan(sh, batch);
-  size_t b = ws_header_bytes(batch, sh.nkv) + (size_t)batch * pl.n_parts * sh.n_q * PART * sizeof(float);
-  if (batch > 1) b += (size_t)batch * sizeof(void*);
-  return b;
+  return ws_header_bytes(batch, sh.nkv) + (size_t)batch * pl.n_parts * sh.n_q * PART * sizeof(float);
 }
 
 extern "C" size_t shard_b200_decode_workspace_bytes(const ShardDecodeShape* shape_host, int32_t batch) {
@@ -550,8 +218,8 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
     if (sh.n_win > 0 && (!s.win_k || !s.win_v)) return SHARD_E_ARG;
     if (sh.n_stream > 0 && (!s.st_k_idx || !s.st_v_idx || !s.st_k_norm || !s.st_v_norm || !s.signs))
       return SHARD_E_ARG;
-    if (((uintptr_t)s.k_coeffs & 3) || ((uintptr_t)s.k_wprep & 15) || ((uintptr_t)s.v_indices & 15) ||
-        ((uintptr_t)s.v_centroids & 7) || ((uintptr_t)s.phase & 7) || ((uintptr_t)s.sink_k & 7) ||
+    if (((uintptr_t)s.k_coeffs & 15) || ((uintptr_t)s.k_wprep & 15) || ((uintptr_t)s.v_indices & 15) ||
+        ((uintptr_t)s.v_centroids & 7) || ((uintptr_t)s.phase & 15) || ((uintptr_t)s.sink_k & 7) ||
         ((uintptr_t)s.sink_v & 7) || ((uintptr_t)s.win_k & 7) || ((uintptr_t)s.win_v & 7) ||
         ((uintptr_t)s.st_k_idx & 3) || ((uintptr_t)s.st_v_idx & 3) || ((uintptr_t)s.signs & 15) ||
         ((uintptr_t)s.v_ch & 7))
@@ -573,39 +241,10 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
   p.n_stream_ctas = pl.n_stream_ctas;
   p.n_parts = pl.n_parts;
 
+  // one launch: the append (if asked for), the split-KV pass and the combine
   dim3 grid(pl.n_parts, sh.nkv, batch);
-  if (decode_mode() == MODE_PIPE) {
-    // one launch: the append (if asked for), the split-KV pass and the combine
-    if (batch == 1 && ((uintptr_t)p.one.k_coeffs & 15)) return SHARD_E_ALIGN;
-    rc = launch_partial_pipe(p, grid, st);
-    if (rc) return rc;
-    SHARD_CHECK_LAUNCH();
-    return SHARD_OK;
-  } else {
-    if (sh.append) {
-      rc = shard_b200_stream_quantize(seqs, batch, sh.nkv, sh.n_stream - 1, codebook, stream);
-      if (rc) return rc;
-    }
-    switch (sh.rank / 32) {
-      case 1: rc = launch_partial<1>(p, grid, st); break;
-      case 2: rc = launch_partial<2>(p, grid, st); break;
-      case 3: rc = launch_partial<3>(p, grid, st); break;
-      case 4: rc = launch_partial<4>(p, grid, st); break;
-      case 5: rc = launch_partial<5>(p, grid, st); break;
-      default: rc = launch_partial<6>(p, grid, st); break;
-    }
-  }
+  rc = launch_partial_pipe(p, grid, st);
   if (rc) return rc;
-  SHARD_CHECK_LAUNCH();
-
-  void** out_table = nullptr;
-  if (batch > 1) {
-    out_table = reinterpret_cast<void**>(reinterpret_cast<unsigned char*>(workspace) + header +
-                                         (size_t)batch * pl.n_parts * sh.n_q * PART * sizeof(float));
-    gather_out_ptrs_kernel<<<(batch + 127) / 128, 128, 0, st>>>(seqs, batch, out_table);
-  }
-  decode_combine_kernel<<<dim3(sh.n_q, batch), HD, 0, st>>>(p.ws, pl.n_parts, pl.n_chunks, sh.n_q, sh.partial_out,
-                                                            out_table, batch == 1 ? p.one.out : nullptr);
   SHARD_CHECK_LAUNCH();
   return SHARD_OK;
 }

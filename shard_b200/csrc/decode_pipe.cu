@@ -44,8 +44,13 @@ constexpr int PP_MISC_BYTES = 1024 + 1024;   // state + barriers, and slack for 
 
 // W holds R + 16 contraction positions (the last 16 carry the mean), in 64-position atoms of 16 KB
 __host__ __device__ constexpr int pp_w_bytes(int nw) { return ((32 * nw + 16 + 63) / 64) * 16384; }
+// staging filled by the bulk copy engine: two tiles of packed coefficients (128 rows x R/2 bytes)
+// and one tile of V codes (128 rows x 32 bytes) per consumer group
+__host__ __device__ constexpr int pp_c_bytes(int nw) { return 128 * 16 * nw; }
+constexpr int PP_VC_BYTES = 128 * VQ_GROUPS;
 __host__ __device__ constexpr int pp_smem_bytes(int nw) {
-  return pp_w_bytes(nw) + PP_STAGES * (PP_V_BYTES + PP_P_BYTES) + PP_Q_BYTES + PP_CB_BYTES + PP_MISC_BYTES;
+  return pp_w_bytes(nw) + PP_STAGES * (PP_V_BYTES + PP_P_BYTES) + PP_Q_BYTES + PP_CB_BYTES + 2 * pp_c_bytes(nw) +
+         PP_STAGES * PP_VC_BYTES + PP_MISC_BYTES;
 }
 
 // single-thread forms (the caller is one elected thread)
@@ -92,7 +97,6 @@ extern "C" int shard_b200_pp_debug_set(long long* buf) { return (int)cudaMemcpyT
 template <int NW>  // rank / 32
 __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(const __grid_constant__ DecodeParams p) {
   constexpr int R = NW * 32;
-  constexpr int KC = R / 8;          // 32-bit words of nibbles per coefficient row
   constexpr int KSTEPS = R / 16 + 1;   // + one step whose A columns are (1, 0, ...) and whose W slice is the mean
   constexpr int W_BYTES = pp_w_bytes(NW);
 
@@ -103,7 +107,9 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   unsigned char* p_s = v_s + PP_STAGES * PP_V_BYTES;               // [3] P operands [16 x 128 tok]
   unsigned char* q_s = p_s + PP_STAGES * PP_P_BYTES;               // Q operand [16 x 128]
   uint2* cbv = reinterpret_cast<uint2*>(q_s + PP_Q_BYTES);         // V codebook
-  float* misc = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(cbv) + PP_CB_BYTES);
+  unsigned char* c_s = reinterpret_cast<unsigned char*>(cbv) + PP_CB_BYTES;   // [2] coefficient tiles
+  unsigned char* vc_s = c_s + 2 * pp_c_bytes(NW);                  // [3] V code tiles
+  float* misc = reinterpret_cast<float*>(vc_s + PP_STAGES * PP_VC_BYTES);
   float* alpha_s = misc;                                           // [3][16]
   float* m_s = misc + 48;                                          // [3][16]
   float* l_s = misc + 96;                                          // [3][16]
@@ -156,26 +162,55 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   auto O_FULL = [&](int s) { return bar0 + 8u * (uint32_t)(6 + s); };     // MMA3 done
   auto T_EMPTY = [&](int s) { return bar0 + 8u * (uint32_t)(9 + s); };    // consumers have drained the stage
   const uint32_t A_EMPTY = bar0 + 8u * 12u;                               // MMA1 has read the A slot
+  const uint32_t W_FULL = bar0 + 8u * 13u;                                // weights have landed
+  auto C_FULL = [&](int b) { return bar0 + 8u * (uint32_t)(14 + b); };    // coefficient tile has landed
+  auto V_FULL = [&](int g) { return bar0 + 8u * (uint32_t)(16 + g); };    // V code tile has landed
+
+  // tiles of this chunk: evenly spread, the first `tiles_rem` chunks get one more
+  const int tile_lo = part * p.tiles_per_chunk + min(part, p.tiles_rem);
+  const int n_my = p.tiles_per_chunk + (part < p.tiles_rem ? 1 : 0);
+  // bulk copies of tile `it` of this chunk: its packed coefficient rows into buffer it % 2, its
+  // V codes into the buffer of consumer group it % 3.  The last tile of the segment may be
+  // short; the rows behind it keep whatever the buffer held (any byte pattern decodes to finite
+  // values, and those rows get zero weight).
+  auto issue_coef = [&](int it) {
+    const int t0 = sh.tok_begin + (tile_lo + it) * 128;
+    const uint32_t bytes = (uint32_t)min(128, sh.tok_end - t0) * (uint32_t)(R / 2);
+    mbar_expect_tx(C_FULL(it & 1), bytes);
+    bulk_g2s(smem_u32(c_s + (it & 1) * pp_c_bytes(NW)), sq.k_coeffs + (size_t)t0 * (R / 2), bytes, C_FULL(it & 1));
+  };
+  auto issue_vcodes = [&](int it) {
+    const int t0 = sh.tok_begin + (tile_lo + it) * 128, g = it % PP_STAGES;
+    const uint32_t bytes = (uint32_t)min(128, sh.tok_end - t0) * (uint32_t)VQ_GROUPS;
+    mbar_expect_tx(V_FULL(g), bytes);
+    bulk_g2s(smem_u32(vc_s + g * PP_VC_BYTES), sq.v_indices + ((size_t)kv * sh.n_comp + t0) * VQ_GROUPS, bytes,
+             V_FULL(g));
+  };
 
   // ---- one-time setup -------------------------------------------------------------------
   {
-    const unsigned char* blob = reinterpret_cast<const unsigned char*>(sq.k_wprep) + (size_t)kv * W_BYTES;
-    const uint4* src = reinterpret_cast<const uint4*>(blob);
-    uint4* dst = reinterpret_cast<uint4*>(w_s);
-    for (int i = tid; i < W_BYTES / 16; i += PP_THREADS) dst[i] = src[i];
+    if (tid == 0) {
+      for (int s = 0; s < PP_STAGES; ++s) {
+        mbar_init(KN_FULL(s), 1); mbar_init(S_FULL(s), 1); mbar_init(O_FULL(s), 1); mbar_init(T_EMPTY(s), 4);
+        mbar_init(V_FULL(s), 1);
+      }
+      mbar_init(A_EMPTY, 1); mbar_init(W_FULL, 1); mbar_init(C_FULL(0), 1); mbar_init(C_FULL(1), 1);
+      *abort_s = 0;
+      fence_mbar_init();
+      // everything the copy engine can fetch ahead: the weights, two coefficient tiles, and the
+      // first V code tile of every consumer group
+      mbar_expect_tx(W_FULL, (uint32_t)W_BYTES);
+      bulk_g2s(smem_u32(w_s), reinterpret_cast<const unsigned char*>(sq.k_wprep) + (size_t)kv * W_BYTES,
+               (uint32_t)W_BYTES, W_FULL);
+      for (int j = 0; j < min(2, n_my); ++j) issue_coef(j);
+      for (int j = 0; j < min(PP_STAGES, n_my); ++j) issue_vcodes(j);
+    }
     if (tid < 256) cbv[tid] = reinterpret_cast<const uint2*>(sq.v_centroids)[tid];
     uint4* z = reinterpret_cast<uint4*>(p_s);
     for (int i = tid; i < (PP_STAGES * PP_P_BYTES + PP_Q_BYTES) / 16; i += PP_THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
 #ifdef SHARD_TC_DEBUG
     if (tid < 48) reinterpret_cast<long long*>(smem + pp_smem_bytes(NW) - 1024 - 512)[tid] = 0;
 #endif
-    if (tid == 0) {
-      for (int s = 0; s < PP_STAGES; ++s) {
-        mbar_init(KN_FULL(s), 1); mbar_init(S_FULL(s), 1); mbar_init(O_FULL(s), 1); mbar_init(T_EMPTY(s), 4);
-      }
-      mbar_init(A_EMPTY, 1);
-      *abort_s = 0;
-    }
   }
   __syncthreads();
   if (tid < HD) {
@@ -211,10 +246,6 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 48] += clock64() - pp_kstart__;
 #endif
 
-  // tiles of this chunk: evenly spread, the first `tiles_rem` chunks get one more
-  const int tile_lo = part * p.tiles_per_chunk + min(part, p.tiles_rem);
-  const int n_my = p.tiles_per_chunk + (part < p.tiles_rem ? 1 : 0);
-
   float acc[16];
 #pragma unroll
   for (int j = 0; j < 16; ++j) acc[j] = 0.f;
@@ -238,8 +269,9 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     unsigned char* v_g = v_s + g * PP_V_BYTES;
     unsigned char* p_g = p_s + g * PP_P_BYTES;
     float* alpha_g = alpha_s + 16 * g;
-    const uint32_t* phase_tab = reinterpret_cast<const uint32_t*>(sq.phase);
-    const uint8_t* vidx = sq.v_indices + (size_t)kv * sh.n_comp * VQ_GROUPS;
+    const uint4* phase_tab = reinterpret_cast<const uint4*>(sq.phase);
+    const uint4* vc_row = reinterpret_cast<const uint4*>(vc_s + g * PP_VC_BYTES + m * VQ_GROUPS);
+    int vc_issued = g < n_my ? 1 : 0;        // V code tiles requested for this group so far
     PP_T0(0);
 #ifdef SHARD_TC_DEBUG
     if (warp != 0) pp_rec__ = nullptr;
@@ -251,19 +283,19 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       const int t0 = sh.tok_begin + (tile_lo + it) * 128;
       const int tok = min(t0 + m, sh.tok_end - 1);
       const bool valid = (t0 + m) < sh.tok_end;
-      const uint4* prow = reinterpret_cast<const uint4*>(phase_tab + (size_t)(tok - sh.tok_begin) * 64);
-      // cos/sin of the row, one uint4 (4 pairs of pairs) per chunk; kept three chunks ahead of use
+      // cos/sin of the row: plane c of the token's block of 32 holds 8 pairs for each of its tokens,
+      // so a warp reads 512 contiguous bytes per plane; kept three chunks ahead of use
+      const int tl = tok - sh.tok_begin;
+      const uint4* prow = phase_tab + (size_t)(tl >> 5) * 512 + (tl & 31);
       uint4 pc[8], ps[8];
-      pc[0] = prow[0]; ps[0] = prow[8];
-      pc[1] = prow[1]; ps[1] = prow[9];
-      pc[2] = prow[2]; ps[2] = prow[10];
+      pc[0] = prow[0 * 32]; ps[0] = prow[8 * 32];
+      pc[1] = prow[1 * 32]; ps[1] = prow[9 * 32];
+      pc[2] = prow[2 * 32]; ps[2] = prow[10 * 32];
 
       PP_T(0);
       bad |= !mbar_wait(KN_FULL(g), par, abort_s);
       tc_fence_after();
       PP_T(1);
-      const uint4 codes0 = *reinterpret_cast<const uint4*>(vidx + (size_t)tok * VQ_GROUPS);
-      const uint4 codes1 = *reinterpret_cast<const uint4*>(vidx + (size_t)tok * VQ_GROUPS + 16);
 
       // ---- rotate: 8 chunks of 8 pairs; K~ goes back in place --------------------------------
       // chunk ch reads c columns [8ch, 8ch+8) and d columns [64+8ch, ...) and writes 4 columns of c'
@@ -273,7 +305,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
         uint32_t cr[8], dr[8];
         tmem_ld_x8(lane_T + 8 * ch, cr);
         tmem_ld_x8(lane_T + 64 + 8 * ch, dr);
-        if (ch + 3 < 8) { pc[ch + 3] = prow[ch + 3]; ps[ch + 3] = prow[8 + ch + 3]; }
+        if (ch + 3 < 8) { pc[ch + 3] = prow[(ch + 3) * 32]; ps[ch + 3] = prow[(8 + ch + 3) * 32]; }
         const uint32_t cos2[4] = {pc[ch].x, pc[ch].y, pc[ch].z, pc[ch].w};
         const uint32_t sin2[4] = {ps[ch].x, ps[ch].y, ps[ch].z, ps[ch].w};
         PP_T(13);
@@ -293,7 +325,9 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       }
       PP_T(2);
       // ---- gather the token's V row (32 codes) into the stage's V tile -------------------------
+      bad |= !mbar_wait(V_FULL(g), par, abort_s);
       {
+        const uint4 codes0 = vc_row[0], codes1 = vc_row[1];
         const uint32_t cw[8] = {codes0.x, codes0.y, codes0.z, codes0.w, codes1.x, codes1.y, codes1.z, codes1.w};
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -311,6 +345,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       bad = named_bar_or(1 + g, 128, bad || *abort_s);
       if (bad) break;                                   // uniform over the group
       if (quad == issuer_quad && lane == 0) {
+        if (it + PP_STAGES < n_my) { issue_vcodes(it + PP_STAGES); ++vc_issued; }   // every lane has read its codes
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
@@ -382,6 +417,9 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       if (lane == 0) mbar_arrive(T_EMPTY(g));
       PP_T(7);
     }
+    // giving up: do not leave while a copy this thread asked for may still be landing
+    if (bad && quad == issuer_quad && lane == 0 && vc_issued > 0)
+      mbar_wait(V_FULL(g), (uint32_t)((vc_issued - 1) & 1), abort_s);
   } else {
     // =============================== unpack warps (+ MMA1 issue) =========================
     constexpr uint32_t IDESC1 = umma_idesc(128, 128, false, false);
@@ -393,27 +431,24 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       const uint32_t ones[8] = {0x00003C00u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
       tmem_st_x8(lane_A + R / 2, ones);
     }
-    uint4 x[NW];
-    {
-      const int tok = min(sh.tok_begin + tile_lo * 128 + m, sh.tok_end - 1);
-      const uint4* row = reinterpret_cast<const uint4*>(sq.k_coeffs + (size_t)tok * (R / 2));
-#pragma unroll
-      for (int i = 0; i < NW; ++i) x[i] = row[i];
-    }
+    int c_issued = min(2, n_my);             // coefficient tiles requested so far (thread 0 asked for the first two)
     PP_T0(1);
 #ifdef SHARD_TC_DEBUG
     if (warp != PP_UNPACK_WARP0) pp_rec__ = nullptr;
 #endif
     bool bad = false;
     for (int it = 0; it < n_my; ++it) {
+      bad |= !mbar_wait(C_FULL(it & 1), (uint32_t)((it >> 1) & 1), abort_s);
       if (it > 0) {
         bad |= !mbar_wait(A_EMPTY, (uint32_t)((it - 1) & 1), abort_s);
         tc_fence_after();
       }
       PP_T(0);
+      const uint4* row = reinterpret_cast<const uint4*>(c_s + (it & 1) * pp_c_bytes(NW) + m * (R / 2));
 #pragma unroll
       for (int i = 0; i < NW; ++i) {
-        const uint32_t wv[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
+        const uint4 xi = row[i];
+        const uint32_t wv[4] = {xi.x, xi.y, xi.z, xi.w};
         uint32_t o[16];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -425,12 +460,6 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
         }
         tmem_st_x16(lane_A + 16 * i, o);
       }
-      if (it + 1 < n_my) {
-        const int tok = min(sh.tok_begin + (tile_lo + it + 1) * 128 + m, sh.tok_end - 1);
-        const uint4* row = reinterpret_cast<const uint4*>(sq.k_coeffs + (size_t)tok * (R / 2));
-#pragma unroll
-        for (int i = 0; i < NW; ++i) x[i] = row[i];
-      }
       tmem_wait_st();
       tc_fence_before();
       bad = named_bar_or(4, 128, bad || *abort_s);
@@ -438,7 +467,9 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       PP_T(1);
       if (quad == 0) {
         if (lane == 0) {
+          if (it + 2 < n_my) { issue_coef(it + 2); ++c_issued; }   // all four warps have read the buffer
           const int s = it % PP_STAGES, use = it / PP_STAGES;
+          if (it == 0) mbar_wait(W_FULL, 0u, abort_s);
           if (use > 0) mbar_wait(T_EMPTY(s), (uint32_t)((use - 1) & 1), abort_s);
           tc_fence_after();
           const uint32_t T = tmem_base + 128u * (uint32_t)s;
@@ -452,6 +483,11 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
         __syncwarp();
         PP_T(2);
       }
+    }
+    // giving up: do not leave while a copy this thread asked for may still be landing
+    if (bad && quad == 0 && lane == 0) {
+      mbar_wait(W_FULL, 0u, abort_s);
+      for (int j = max(0, c_issued - 2); j < c_issued; ++j) mbar_wait(C_FULL(j & 1), (uint32_t)((j >> 1) & 1), abort_s);
     }
   }
 

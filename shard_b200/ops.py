@@ -130,11 +130,19 @@ def vq_assign(x, centroids, want_i64=True):
 
 
 # --------------------------------------------------------------------------- decode
+def phase_table_numel(n):
+    """fp16 elements of the phase table of `n` tokens (tokens are padded to blocks of 32)."""
+    return max(_lib.load().shard_b200_phase_table_bytes(int(n)) // 2, 128 * 32)
+
+
 def phase_table(compress_start, pos_q, n, inv_freq, out=None):
-    """fp16 (cos, sin) of fp32(compress_start + t - pos_q) * inv_freq for t < n: (n, 64, 2)."""
+    """fp16 cos / sin of fp32(compress_start + t - pos_q) * inv_freq for t < n, in the
+    block-of-32-tokens plane layout the decode kernel reads (flat fp16 tensor)."""
     require_cuda(inv_freq)
     if out is None:
-        out = torch.empty(max(n, 1), 64, 2, dtype=torch.float16, device=inv_freq.device)
+        out = torch.empty(phase_table_numel(n), dtype=torch.float16, device=inv_freq.device)
+    elif out.numel() < phase_table_numel(n):
+        raise _lib.ShardError("phase table buffer too small")
     check(_lib.load().shard_b200_phase_table(int(compress_start), int(pos_q), int(n),
                                              ptr(_c(inv_freq, torch.float32)), ptr(out), cur_stream()),
           "phase_table")

@@ -142,7 +142,7 @@ class BatchedDecoder:
         self.new_v = torch.zeros(self.n_layers, S, self.nkv, self.hd, dtype=torch.float16, device=dev)
         self.codebook = get_codebook(self.hd, 8, dev)
         self.inv_freq = c0._inv_freq(dev)
-        self.phase = torch.empty(max(self.n_comp, 1), 64, 2, dtype=torch.float16, device=dev)
+        self.phase = torch.empty(ops.phase_table_numel(self.n_comp), dtype=torch.float16, device=dev)
         self.tables = []
         self._keep = []
         for li in range(self.n_layers):

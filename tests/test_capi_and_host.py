@@ -51,7 +51,7 @@ def test_argument_validation_without_gpu():
     sh = ops.make_shape(32, 8, 192, 32700, 0, 32700, 4, 64, 255, 33023)
     need = lib.shard_b200_decode_workspace_bytes(C.byref(sh), 1)
     assert 0 < need < (8 << 20)
-    assert lib.shard_b200_wprep_bytes(8, 192) == 8 * 4 * 16384 + 8 * 13 * 4096
+    assert lib.shard_b200_wprep_bytes(8, 192) == 8 * 4 * 16384
     assert lib.shard_b200_wprep_bytes(8, 200) == 0
     seq = _lib.ShardSeq()
     assert lib.shard_b200_decode_attn(C.addressof(seq), 1, C.byref(sh), None, None, None, 0, None) == -1
