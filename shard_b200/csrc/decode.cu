@@ -34,7 +34,7 @@ int launch_prepare_pipe(const void* basis, const void* cscale, const void* mean,
 int launch_partial_pipe(const DecodeParams& p, dim3 grid, cudaStream_t st);
 
 struct DecodePlan {
-  int n_chunks, tiles_per_chunk, tiles_rem, n_fp16_ctas, n_stream_ctas, n_parts;
+  int n_chunks, tiles_per_chunk, tiles_rem, n_row_parts, n_parts, grid_x;
 };
 
 static DecodePlan make_plan(const ShardDecodeShape& sh, int batch) {
@@ -51,9 +51,18 @@ static DecodePlan make_plan(const ShardDecodeShape& sh, int batch) {
     pl.tiles_per_chunk = n_tiles / chunks;
     pl.tiles_rem = n_tiles % chunks;
   }
-  pl.n_fp16_ctas = (sh.n_sink + sh.n_win) > 0 ? 1 : 0;
-  pl.n_stream_ctas = (sh.n_stream + STREAM_TOK_PER_CTA - 1) / STREAM_TOK_PER_CTA;
-  pl.n_parts = pl.n_chunks + pl.n_fp16_ctas + pl.n_stream_ctas;
+  // the fp16 / streamed rows ride along in the chunk CTAs (dealt out row by row, handled while a
+  // CTA waits for its first tile); only a launch without a middle gets CTAs just for them
+  const int n_rows = sh.n_sink + sh.n_win + sh.n_stream;
+  if (n_rows > 0) {
+    pl.n_row_parts = pl.n_chunks;
+    if (pl.n_chunks == 0) {
+      pl.n_row_parts = (n_rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
+      if (pl.n_row_parts > MAX_ROW_CTAS) pl.n_row_parts = MAX_ROW_CTAS;
+    }
+  }
+  pl.n_parts = pl.n_chunks + pl.n_row_parts;
+  pl.grid_x = pl.n_chunks > 0 ? pl.n_chunks : pl.n_row_parts;
   return pl;
 }
 
@@ -237,12 +246,12 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
   p.n_chunks = pl.n_chunks;
   p.tiles_per_chunk = pl.tiles_per_chunk;
   p.tiles_rem = pl.tiles_rem;
-  p.n_fp16_ctas = pl.n_fp16_ctas;
-  p.n_stream_ctas = pl.n_stream_ctas;
+  p.n_row_parts = pl.n_row_parts;
   p.n_parts = pl.n_parts;
+  p.n_ctas = pl.grid_x;
 
   // one launch: the append (if asked for), the split-KV pass and the combine
-  dim3 grid(pl.n_parts, sh.nkv, batch);
+  dim3 grid(pl.grid_x, sh.nkv, batch);
   rc = launch_partial_pipe(p, grid, st);
   if (rc) return rc;
   SHARD_CHECK_LAUNCH();

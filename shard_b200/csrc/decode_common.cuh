@@ -7,7 +7,8 @@
 
 namespace shard {
 
-constexpr int STREAM_TOK_PER_CTA = 32;
+constexpr int ROWS_PER_CTA = 32;        // rows per CTA when a launch has no middle segment
+constexpr int MAX_ROW_CTAS = 18;
 
 struct DecodeParams {
   ShardSeq one;
@@ -18,12 +19,13 @@ struct DecodeParams {
   float* ws;
   int* status;          // device word set non-zero when a bounded wait gave up
   int* tickets;         // [batch][nkv] arrival counters of the fused combine (zero between calls)
-  int n_chunks;         // CTAs (per KV head) that walk the compressed middle
+  int n_chunks;         // CTAs (per KV head) that walk the compressed middle (0: there is no middle)
   int tiles_per_chunk;
-  int tiles_rem;        // pipelined kernel: the first tiles_rem chunks walk one tile more
-  int n_fp16_ctas;      // 1 if there are sink / window rows
-  int n_stream_ctas;
-  int n_parts;          // n_chunks + n_fp16_ctas + n_stream_ctas
+  int tiles_rem;        // the first tiles_rem chunks walk one tile more
+  int n_row_parts;      // CTAs (per KV head) that share the fp16 / streamed rows: the chunk CTAs
+                        // themselves when there is a middle, else CTAs of their own; 0: no rows
+  int n_parts;          // records per (sequence, query head): n_chunks rotated-space + n_row_parts standard
+  int n_ctas;           // CTAs per (sequence, KV head) = gridDim.x
 };
 
 struct SoftmaxState {
@@ -98,12 +100,10 @@ __device__ __forceinline__ void stage_query(const ShardSeq& sq, int kv, int pos_
 }
 
 // Fused append: the CTA that owns streamed row n_stream-1 first quantises the step's new
-// K/V vector of its KV head into that row (warp 0: K, warp 1: V).  The caller synchronises
+// K/V vector of its KV head into that row (one warp each for K and V).  The caller synchronises
 // the CTA afterwards; the rows are then read back with L2-coherent loads.
 __device__ __forceinline__ void append_new_token(const ShardSeq& sq, const ShardDecodeShape& sh, int kv,
-                                                 const float* __restrict__ cbs, int warp, int lane) {
-  if (warp >= 2) return;
-  const bool is_v = warp == 1;
+                                                 const float* __restrict__ cbs, bool is_v, int lane) {
   const size_t row = (size_t)(sh.n_stream - 1) * sh.nkv + kv;
   const __half* src = reinterpret_cast<const __half*>(is_v ? sq.new_v : sq.new_k) + kv * HD;
   uint8_t* idx_out = (is_v ? sq.st_v_idx : sq.st_k_idx) + row * HD;
@@ -111,22 +111,23 @@ __device__ __forceinline__ void append_new_token(const ShardSeq& sq, const Shard
   quantize_vec_warp(src, sq.signs, cbs, idx_out, norm_out, lane);
 }
 
-// fp16 rows (sink + window) or streamed rows [u_lo, u_hi): one warp per token, lane owns
-// channels 4*lane..+3.  `qr` is the query as given (fp32 copy in shared memory), `cbs` the
-// stream codebook in shared memory (streamed rows only).
-template <int NWARPS>
+// Rows outside the compressed middle, in one index space: u < n_sink + n_win is an fp16 row
+// (sink rows first), the rest are streamed rows.  A warp takes rows u_first, u_first + u_step, ...;
+// lane owns channels 4*lane..+3.  `qr` is the query as given (fp32 copy in shared memory), `cbs`
+// the stream codebook in shared memory (needed for streamed rows only).
 __device__ __forceinline__ void process_rows(SoftmaxState& st, const ShardSeq& sq, const ShardDecodeShape& sh,
-                                             int kv, bool is_fp16, int u_lo, int u_hi,
-                                             const float* __restrict__ qr, const float* __restrict__ cbs,
-                                             int warp, int lane) {
+                                             int kv, int u_first, int u_step,
+                                             const float* __restrict__ qr, const float* __restrict__ cbs, int lane) {
+  const int n_fp = sh.n_sink + sh.n_win, n_rows = n_fp + sh.n_stream;
+  if (u_first >= n_rows) return;
   float4 sg = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (!is_fp16) sg = *reinterpret_cast<const float4*>(sq.signs + 4 * lane);
+  if (sh.n_stream > 0) sg = *reinterpret_cast<const float4*>(sq.signs + 4 * lane);
   float4 qv[GQA];
 #pragma unroll
   for (int h = 0; h < GQA; ++h) qv[h] = *reinterpret_cast<const float4*>(qr + h * HD + 4 * lane);
-  for (int u = u_lo + warp; u < u_hi; u += NWARPS) {
+  for (int u = u_first; u < n_rows; u += u_step) {
     float kx[4], vx[4];
-    if (is_fp16) {
+    if (u < n_fp) {
       const bool in_sink = u < sh.n_sink;
       const int r = in_sink ? u : u - sh.n_sink;
       const int rows = in_sink ? sh.n_sink : sh.n_win;
@@ -142,7 +143,7 @@ __device__ __forceinline__ void process_rows(SoftmaxState& st, const ShardSeq& s
       kx[0] = k01.x; kx[1] = k01.y; kx[2] = k23.x; kx[3] = k23.y;
       vx[0] = v01.x; vx[1] = v01.y; vx[2] = v23.x; vx[3] = v23.y;
     } else {
-      const size_t row = (size_t)u * sh.nkv + kv;
+      const size_t row = (size_t)(u - n_fp) * sh.nkv + kv;
       const float kn = __half2float(__ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(sq.st_k_norm) + row)));
       const float vn = __half2float(__ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(sq.st_v_norm) + row)));
       stream_dequant_lane4(sq.st_k_idx + row * HD, kn, cbs, sg, lane, kx);
@@ -161,43 +162,46 @@ __device__ __forceinline__ void process_rows(SoftmaxState& st, const ShardSeq& s
   }
 }
 
-// Merge the per-warp softmax states of a CTA (lane owns channels 4*lane..+3, m/l are
-// warp-uniform) and write one record per head.  `scratch` needs NWARPS*4*130 floats and
-// must not be in use; the caller has synchronised the CTA before the call.
+// Merge of per-warp softmax states (lane owns channels 4*lane..+3, m/l are warp-uniform) into one
+// record per head, in two steps with a barrier of the caller's choice in between:
+// partial_store by every one of the NWARPS warps (index `w`), then partial_merge by 128 threads
+// (d = 0..127).  `scratch` needs NWARPS*4*130 floats.
 template <int NWARPS>
-__device__ __forceinline__ void emit_partial(const SoftmaxState& st, float* __restrict__ scratch,
-                                             float* __restrict__ rec_base, int tid, int warp, int lane) {
+__device__ __forceinline__ void partial_store(const SoftmaxState& st, float* __restrict__ scratch, int w, int lane) {
   float* mw = scratch;
   float* lw = mw + NWARPS * GQA;
   float* aw = lw + NWARPS * GQA;
   if (lane == 0) {
 #pragma unroll
-    for (int h = 0; h < GQA; ++h) { mw[warp * GQA + h] = st.m[h]; lw[warp * GQA + h] = st.l[h]; }
+    for (int h = 0; h < GQA; ++h) { mw[w * GQA + h] = st.m[h]; lw[w * GQA + h] = st.l[h]; }
   }
 #pragma unroll
   for (int h = 0; h < GQA; ++h)
-    *reinterpret_cast<float4*>(aw + (warp * GQA + h) * HD + 4 * lane) =
+    *reinterpret_cast<float4*>(aw + (w * GQA + h) * HD + 4 * lane) =
         make_float4(st.acc[h][0], st.acc[h][1], st.acc[h][2], st.acc[h][3]);
-  __syncthreads();
-  if (tid < HD) {
-    const int d = tid;
+}
+
+template <int NWARPS>
+__device__ __forceinline__ void partial_merge(const float* scratch, float* __restrict__ rec_base, int d) {
+  const float* mw = scratch;
+  const float* lw = mw + NWARPS * GQA;
+  const float* aw = lw + NWARPS * GQA;
 #pragma unroll
-    for (int h = 0; h < GQA; ++h) {
-      float M = neg_inf();
+  for (int h = 0; h < GQA; ++h) {
+    float M = neg_inf();
 #pragma unroll
-      for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, mw[w * GQA + h]);
-      float L = 0.f, a = 0.f;
+    for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, mw[w * GQA + h]);
+    float L = 0.f, a = 0.f;
 #pragma unroll
-      for (int w = 0; w < NWARPS; ++w) {
-        const float mwv = mw[w * GQA + h];
-        const float wt = (mwv == neg_inf()) ? 0.f : exp2f((mwv - M) * LOG2E);
-        L = fmaf(wt, lw[w * GQA + h], L);
-        a = fmaf(wt, aw[(w * GQA + h) * HD + d], a);
-      }
-      float* rec = rec_base + h * PART;
-      if (d == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
-      rec[4 + d] = a;
+    for (int w = 0; w < NWARPS; ++w) {
+      const float mwv = mw[w * GQA + h];
+      const float wt = (mwv == neg_inf()) ? 0.f : exp2f((mwv - M) * LOG2E);
+      L = fmaf(wt, lw[w * GQA + h], L);
+      a = fmaf(wt, aw[(w * GQA + h) * HD + d], a);
     }
+    float* rec = rec_base + h * PART;
+    if (d == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
+    rec[4 + d] = a;
   }
 }
 
@@ -205,8 +209,8 @@ __device__ __forceinline__ void emit_partial(const SoftmaxState& st, float* __re
 // Each takes a ticket; the CTA that draws the last one sees all records of that KV head
 // (release/acquire through the fences around the ticket), merges them for the head's four
 // query heads exactly as decode_combine_kernel does (same order, same operations), and puts
-// the counter back to zero for the next call.  `sm` needs GQA*HD floats that are free;
-// NTHREADS >= GQA*HD.  Thread tid handles head tid/128, channel tid%128.
+// the counter back to zero for the next call.  `sm` needs GQA*HD + 2*GQA*n_parts floats that
+// are free; NTHREADS >= GQA*HD.  Thread tid handles head tid/128, channel tid%128.
 template <int NTHREADS>
 __device__ __forceinline__ void ticket_combine(const DecodeParams& p, const ShardSeq& sq, int kv, int b,
                                                float* sm_raw, int tid) {
@@ -217,7 +221,7 @@ __device__ __forceinline__ void ticket_combine(const DecodeParams& p, const Shar
   __syncthreads();
   if (tid == 0) {
     int* ctr = p.tickets + b * p.sh.nkv + kv;
-    const int last = atomicAdd(ctr, 1) == p.n_parts - 1;
+    const int last = atomicAdd(ctr, 1) == p.n_ctas - 1;
     if (last) atomicExch(ctr, 0);
     last_s = last;
   }
@@ -226,21 +230,29 @@ __device__ __forceinline__ void ticket_combine(const DecodeParams& p, const Shar
   __threadfence();
   const bool active = tid < GQA * HD;
   const int n_q = p.sh.n_q, n_parts = p.n_parts, n_rot = p.n_chunks;
-  const int h = kv * GQA + ((tid >> 7) & (GQA - 1)), d = tid & (HD - 1);
-  const float* base = p.ws + ((size_t)b * n_parts * n_q + h) * PART;
+  const int hl = (tid >> 7) & (GQA - 1), h = kv * GQA + hl, d = tid & (HD - 1);
+  const float* base0 = p.ws + ((size_t)b * n_parts * n_q + (size_t)kv * GQA) * PART;
   const size_t pstride = (size_t)n_q * PART;
+  // (max, sum-exp) of every part of the four heads: one load per thread, all in flight together
+  volatile float* ms = sm + GQA * HD;                 // [GQA][n_parts]
+  volatile float* ls = ms + GQA * n_parts;            // [GQA][n_parts]
+  for (int idx = tid; idx < GQA * n_parts; idx += NTHREADS) {
+    const int hh = idx / n_parts, pi = idx - hh * n_parts;
+    const float* rec = base0 + pi * pstride + hh * PART;
+    ms[idx] = __ldcg(rec);
+    ls[idx] = __ldcg(rec + 1);
+  }
+  __syncthreads();
   float M = neg_inf(), L = 0.f, rot = 0.f, stdv = 0.f;
   if (active) {
-#pragma unroll 8
-    for (int pi = 0; pi < n_parts; ++pi) M = fmaxf(M, __ldcg(base + pi * pstride));
-#pragma unroll 8
+    for (int pi = 0; pi < n_parts; ++pi) M = fmaxf(M, ms[hl * n_parts + pi]);
+    const float* accp = base0 + hl * PART + 4 + d;
+#pragma unroll 12
     for (int pi = 0; pi < n_parts; ++pi) {
-      const float* rec = base + pi * pstride;
-      const float m = __ldcg(rec);
-      const float l = __ldcg(rec + 1);
-      const float a = __ldcg(rec + 4 + d);
+      const float a = __ldcg(accp + pi * pstride);
+      const float m = ms[hl * n_parts + pi];
       const float wt = (m == neg_inf()) ? 0.f : exp2f((m - M) * LOG2E);
-      L = fmaf(wt, l, L);
+      L = fmaf(wt, ls[hl * n_parts + pi], L);
       if (pi < n_rot) rot = fmaf(wt, a, rot); else stdv = fmaf(wt, a, stdv);
     }
   }

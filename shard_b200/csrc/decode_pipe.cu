@@ -36,6 +36,7 @@ constexpr int PP_COL_A = 384;         // A operand slot: R/2 coefficient columns
 constexpr int PP_COL_S = 64;          // within a stage
 constexpr int PP_COL_O = 80;
 constexpr int PP_V_BYTES = 32768, PP_P_BYTES = 4096, PP_Q_BYTES = 4096, PP_CB_BYTES = 2048;
+constexpr int PP_ROWQ_BYTES = (GQA * HD + 256) * 4;   // queries as given + stream codebook, for the row path
 #ifdef SHARD_TC_DEBUG
 constexpr int PP_MISC_BYTES = 1024 + 1024 + 512;   // + per-role timing accumulators
 #else
@@ -49,8 +50,8 @@ __host__ __device__ constexpr int pp_w_bytes(int nw) { return ((32 * nw + 16 + 6
 __host__ __device__ constexpr int pp_c_bytes(int nw) { return 128 * 16 * nw; }
 constexpr int PP_VC_BYTES = 128 * VQ_GROUPS;
 __host__ __device__ constexpr int pp_smem_bytes(int nw) {
-  return pp_w_bytes(nw) + PP_STAGES * (PP_V_BYTES + PP_P_BYTES) + PP_Q_BYTES + PP_CB_BYTES + 2 * pp_c_bytes(nw) +
-         PP_STAGES * PP_VC_BYTES + PP_MISC_BYTES;
+  return pp_w_bytes(nw) + PP_STAGES * (PP_V_BYTES + PP_P_BYTES) + PP_Q_BYTES + PP_CB_BYTES + PP_ROWQ_BYTES +
+         2 * pp_c_bytes(nw) + PP_STAGES * PP_VC_BYTES + PP_MISC_BYTES;
 }
 
 // single-thread forms (the caller is one elected thread)
@@ -72,6 +73,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // over the participants.  The roles use it to agree on giving up: a warp whose bounded wait
 // failed never leaves its siblings alone at a barrier -- everybody reaches the barrier, learns
 // the combined flag and leaves the tile loop together.
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
 __device__ __forceinline__ bool named_bar_or(int id, int count, bool flag) {
   uint32_t out;
   asm volatile(
@@ -107,7 +111,9 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   unsigned char* p_s = v_s + PP_STAGES * PP_V_BYTES;               // [3] P operands [16 x 128 tok]
   unsigned char* q_s = p_s + PP_STAGES * PP_P_BYTES;               // Q operand [16 x 128]
   uint2* cbv = reinterpret_cast<uint2*>(q_s + PP_Q_BYTES);         // V codebook
-  unsigned char* c_s = reinterpret_cast<unsigned char*>(cbv) + PP_CB_BYTES;   // [2] coefficient tiles
+  float* qr_s = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(cbv) + PP_CB_BYTES);   // queries as given [4][128]
+  float* cbs_s = qr_s + GQA * HD;                                  // stream codebook [256]
+  unsigned char* c_s = reinterpret_cast<unsigned char*>(cbs_s + 256);         // [2] coefficient tiles
   unsigned char* vc_s = c_s + 2 * pp_c_bytes(NW);                  // [3] V code tiles
   float* misc = reinterpret_cast<float*>(vc_s + PP_STAGES * PP_VC_BYTES);
   float* alpha_s = misc;                                           // [3][16]
@@ -126,31 +132,38 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
 
 #ifdef SHARD_TC_DEBUG
   const long long pp_kstart__ = clock64();
+  if (g_pp_debug && tid == 0) {
+    unsigned long long gt; unsigned smid;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+    g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 50] = (long long)gt;
+    g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 52] = smid;
+  }
 #endif
-  if (part >= p.n_chunks) {
-    // sink + window rows, or streamed rows: warp-per-token path
+  const int n_rows = sh.n_sink + sh.n_win + sh.n_stream;
+  // the CTA that owns the newest streamed row quantises it before anybody reads the stream
+  const bool append_here = sh.append && p.n_row_parts > 0 && (n_rows - 1) % p.n_row_parts == part;
+  float* rec_rows = p.ws + (((size_t)blockIdx.z * p.n_parts + p.n_chunks + part) * sh.n_q + (size_t)kv * GQA) * PART;
+
+  if (p.n_chunks == 0) {
+    // a launch without a middle segment: every CTA only attends to its share of the rows
     float* qn = reinterpret_cast<float*>(smem);
     float* qr = qn + GQA * HD;
     float* cbs = qr + GQA * HD;
     float* scratch = cbs + 256;
-    const bool is_fp16 = part < p.n_chunks + p.n_fp16_ctas;
-    if (!is_fp16) for (int i = tid; i < 256; i += PP_THREADS) cbs[i] = p.codebook[i];
+    if (sh.n_stream > 0) for (int i = tid; i < 256; i += PP_THREADS) cbs[i] = p.codebook[i];
     if (tid < HD) stage_query(sq, kv, sh.pos_q, p.inv_freq, tid, qn, qr);
     __syncthreads();
-    int u_lo = 0, u_hi = sh.n_sink + sh.n_win;
-    if (!is_fp16) {
-      u_lo = (part - p.n_chunks - p.n_fp16_ctas) * STREAM_TOK_PER_CTA;
-      u_hi = min(u_lo + STREAM_TOK_PER_CTA, sh.n_stream);
-    }
-    if (!is_fp16 && sh.append && u_hi == sh.n_stream) {   // this CTA owns the newest streamed row
-      append_new_token(sq, sh, kv, cbs, warp, lane);
+    if (append_here) {
+      if (warp < 2) append_new_token(sq, sh, kv, cbs, warp == 1, lane);
       __syncthreads();
     }
     SoftmaxState st;
     softmax_init(st);
-    process_rows<PP_WARPS>(st, sq, sh, kv, is_fp16, u_lo, u_hi, qr, cbs, warp, lane);
+    process_rows(st, sq, sh, kv, part + p.n_row_parts * warp, p.n_row_parts * PP_WARPS, qr, cbs, lane);
+    partial_store<PP_WARPS>(st, scratch, warp, lane);
     __syncthreads();
-    emit_partial<PP_WARPS>(st, scratch, rec_base, tid, warp, lane);
+    if (tid < HD) partial_merge<PP_WARPS>(scratch, rec_rows, tid);
     ticket_combine<PP_THREADS>(p, sq, kv, blockIdx.z, scratch, tid);
     return;
   }
@@ -206,6 +219,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       for (int j = 0; j < min(PP_STAGES, n_my); ++j) issue_vcodes(j);
     }
     if (tid < 256) cbv[tid] = reinterpret_cast<const uint2*>(sq.v_centroids)[tid];
+    else if (sh.n_stream > 0) cbs_s[tid - 256] = p.codebook[tid - 256];
     uint4* z = reinterpret_cast<uint4*>(p_s);
     for (int i = tid; i < (PP_STAGES * PP_P_BYTES + PP_Q_BYTES) / 16; i += PP_THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
 #ifdef SHARD_TC_DEBUG
@@ -231,8 +245,11 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       const __half rot = (d < 64) ? __hneg(other) : other;
       const __half un = __hsub(__hmul(x, c16), __hmul(rot, s16));
       *reinterpret_cast<__half*>(q_s + (kk >> 6) * 2048 + sw128_off(h, (kk >> 3) & 7) + (kk & 7) * 2) = un;
+      qr_s[h * HD + d] = __half2float(x);
     }
   }
+  // fused append by two otherwise idle warps; the barrier below orders it before the reads
+  if (append_here && (warp == 14 || warp == 15)) append_new_token(sq, sh, kv, cbs_s, warp == 15, lane);
   if (warp == PP_UNPACK_WARP0) {
     tmem_alloc(smem_u32(tmem_slot), PP_TMEM_COLS);
     tmem_relinquish();
@@ -272,6 +289,23 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     const uint4* phase_tab = reinterpret_cast<const uint4*>(sq.phase);
     const uint4* vc_row = reinterpret_cast<const uint4*>(vc_s + g * PP_VC_BYTES + m * VQ_GROUPS);
     int vc_issued = g < n_my ? 1 : 0;        // V code tiles requested for this group so far
+
+    if (p.n_row_parts > 0) {
+      // This CTA's share of the fp16 / streamed rows (row u belongs to CTA u % n_row_parts), one
+      // warp per row, while the first tile is still on its way.  The twelve warps' states are
+      // merged through group 0's V tile, which nothing has written yet, into a record of its own
+      // (standard V space; the middle's record is in rotated space).
+      SoftmaxState st;
+      softmax_init(st);
+      process_rows(st, sq, sh, kv, part + p.n_row_parts * warp, p.n_row_parts * PP_CONS_WARPS, qr_s, cbs_s, lane);
+      float* scratch = reinterpret_cast<float*>(v_s);
+      partial_store<PP_CONS_WARPS>(st, scratch, warp, lane);
+      named_bar_sync(5, PP_CONS_WARPS * 32);
+      if (g == 0) {
+        partial_merge<PP_CONS_WARPS>(scratch, rec_rows, m);
+        named_bar_sync(1, 128);                       // all of group 0 has read the scratch before any of it gathers
+      }
+    }
     PP_T0(0);
 #ifdef SHARD_TC_DEBUG
     if (warp != 0) pp_rec__ = nullptr;
@@ -535,6 +569,11 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   ticket_combine<PP_THREADS>(p, sq, kv, blockIdx.z, reinterpret_cast<float*>(w_s), tid);
 #ifdef SHARD_TC_DEBUG
   if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 49] += clock64() - pp_kstart__;
+  if (g_pp_debug && tid == 0) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+    g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 51] = (long long)gt;
+  }
   if (g_pp_debug && tid < 48)
     g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + tid] += reinterpret_cast<long long*>(smem + pp_smem_bytes(NW) - 1024 - 512)[tid];
 #endif
