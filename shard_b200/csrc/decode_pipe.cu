@@ -21,6 +21,8 @@
 // place by K~ (fp16x2, columns 0-63 of the stage), scores (64-79) and the tile's P.V (80-95).
 // Every hand-over is an mbarrier; every wait is bounded and raises the CTA's abort flag when it
 // gives up, after which all roles drain, tensor memory is freed and the status word is set.
+#include <cstdlib>
+
 #include "decode_common.cuh"
 #include "tcgen05.cuh"
 
@@ -145,8 +147,10 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   const bool append_here = sh.append && p.n_row_parts > 0 && (n_rows - 1) % p.n_row_parts == part;
   float* rec_rows = p.ws + (((size_t)blockIdx.z * p.n_parts + p.n_chunks + part) * sh.n_q + (size_t)kv * GQA) * PART;
 
+  griddep_launch();
   if (p.n_chunks == 0) {
     // a launch without a middle segment: every CTA only attends to its share of the rows
+    griddep_wait();
     float* qn = reinterpret_cast<float*>(smem);
     float* qr = qn + GQA * HD;
     float* cbs = qr + GQA * HD;
@@ -226,6 +230,10 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     if (tid < 48) reinterpret_cast<long long*>(smem + pp_smem_bytes(NW) - 1024 - 512)[tid] = 0;
 #endif
   }
+  // Up to here only tensors that no decode call ever writes were touched (weights, coefficients,
+  // V codes, codebooks).  The query, the new token, the stream rows, the phase table, the scratch
+  // and the output may come from, or still be in use by, the call before this one.
+  griddep_wait();
   __syncthreads();
   if (tid < HD) {
     // un-rotated query (fp16 arithmetic as the reference) -> Q operand rows 0..3; element of pair i
@@ -629,8 +637,27 @@ static int launch_pipe_one(const DecodeParams& p, dim3 grid, cudaStream_t st) {
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  decode_partial_pipe_kernel<NW><<<grid, PP_THREADS, SMEM, st>>>(p);
-  return 0;
+  // Programmatic dependent launch: when the kernel in front of this one in the stream is another
+  // decode launch, this one's CTAs move onto SMs as that one's CTAs retire and set up (barriers,
+  // first bulk copies) while its last CTAs finish; griddep_wait in the kernel keeps the order of
+  // everything that matters.  SHARD_B200_PDL=0 in the environment turns it off.
+  static int use_pdl = -1;
+  if (use_pdl < 0) {
+    const char* e = getenv("SHARD_B200_PDL");
+    use_pdl = (e && e[0] == '0') ? 0 : 1;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(PP_THREADS);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_partial_pipe_kernel<NW>, p);
+  return e == cudaSuccess ? 0 : (int)e;
 }
 
 int launch_partial_pipe(const DecodeParams& p, dim3 grid, cudaStream_t st) {

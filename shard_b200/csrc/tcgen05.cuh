@@ -38,6 +38,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   *abort_flag = 1;
   return false;
 }
+// Programmatic dependent launch.  `griddep_launch` lets the next kernel in the stream (if it was
+// launched with the programmatic-serialization attribute) place its CTAs on SMs as they become
+// free; `griddep_wait` blocks until every kernel this one depends on has finished and its memory
+// is visible.  Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 // makes freshly initialised mbarriers visible to the copy engine and the tensor core
 __device__ __forceinline__ void fence_mbar_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
