@@ -5,7 +5,7 @@
 computation -- scores on packed int4 PCA coefficients through the per-pair
 relative-phase RoPE identity, the fp16 sink/window segments, the 8-bit streamed
 tokens, one global softmax, the VQ-V weighted sum and the single inverse
-Hadamard -- is two kernel launches of libshard_b200.so.
+Hadamard -- is one kernel launch of libshard_b200.so.
 """
 from __future__ import annotations
 
@@ -54,6 +54,39 @@ def _seq_record(gc, dev):
     return seq
 
 
+class _Launch:
+    """Per-layer launch state that does not change from step to step: the sequence record, the
+    shape record (only n_stream / pos_q / append are touched per step), workspace need and
+    the constant device pointers."""
+    __slots__ = ("key", "seq", "shape", "need", "inv_ptr", "cb", "cb_ptr")
+
+
+def _launch_state(gc, cache, dev, nkv, n_q, t0, t1, with_fp16_segments, partial_out):
+    n_sink = gc["sink_k"].shape[2] if with_fp16_segments else 0
+    n_win = gc["win_k"].shape[2] if with_fp16_segments else 0
+    key = (t0, t1, n_sink, n_win, bool(partial_out), gc["n_compress"], gc["k_rank_kernel"], str(dev))
+    ls = gc.get("_launch")
+    if ls is None or ls.key != key:
+        ls = _Launch()
+        ls.key = key
+        ls.seq = _seq_record(gc, dev)
+        ls.shape = ops.make_shape(n_q, nkv, gc["k_rank_kernel"], gc["n_compress"], t0, t1, n_sink, n_win, 0, 0,
+                                  partial_out)
+        # With a middle segment the scratch size does not depend on the number of rows (they ride
+        # along in the middle's CTAs), only on whether there are any; without one it is asked for
+        # per call.
+        ls.need = 0
+        if t1 > t0:
+            probe = ops.make_shape(n_q, nkv, gc["k_rank_kernel"], gc["n_compress"], t0, t1, n_sink, n_win, 1, 0,
+                                   partial_out)
+            ls.need = ops.decode_workspace_bytes(probe, 1)
+        ls.inv_ptr = ptr(cache._inv_freq(dev))
+        ls.cb = get_codebook(128, 8, dev)
+        ls.cb_ptr = ptr(ls.cb)
+        gc["_launch"] = ls
+    return ls
+
+
 def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_fp16_segments=True, out=None):
     """Run the fused decode for one layer.
 
@@ -63,7 +96,8 @@ def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_f
     """
     gc = layer._gpu_compressed
     cache = layer._cache_ref
-    _lib.require_cuda(q_rope)
+    if not q_rope.is_cuda:
+        raise _lib.ShardError("shard_b200 kernels need CUDA tensors; there is no CPU fallback")
     B, n_q, s_q, hd = q_rope.shape
     nkv = cache._n_kv_heads
     if B != 1 or s_q != 1:
@@ -75,54 +109,61 @@ def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_f
     if "decode_k" in gc:
         raise NotImplementedError("fp16 decode buffer (non-streaming append) is served by the dequantised path")
     dev = q_rope.device
-    n_comp = gc["n_compress"]
-    t0, t1 = (0, n_comp) if tok_range is None else tok_range
-    n_sink = gc["sink_k"].shape[2] if with_fp16_segments else 0
-    n_win = gc["win_k"].shape[2] if with_fp16_segments else 0
+    t0, t1 = (0, gc["n_compress"]) if tok_range is None else tok_range
+    ls = _launch_state(gc, cache, dev, nkv, n_q, t0, t1, with_fp16_segments, partial_out)
     n_stream = gc.get("stream_n", 0) if with_fp16_segments else 0
     pending = gc.pop("_pending", None)
     if pending is not None and (not with_fp16_segments or pending[2] != n_stream - 1):
         gc["_pending"] = pending
         layer._flush_pending()
         pending = None
-    seq = _seq_record(gc, dev)
+    seq, shape = ls.seq, ls.shape
+    if n_stream > 0:
+        kbuf = gc["k_idx_buf"]
+        if seq.st_k_idx != kbuf.data_ptr():            # the stream buffers were (re)allocated
+            seq.st_k_idx, seq.st_v_idx = kbuf.data_ptr(), gc["v_idx_buf"].data_ptr()
+            seq.st_k_norm, seq.st_v_norm = gc["k_norm_buf"].data_ptr(), gc["v_norm_buf"].data_ptr()
+            seq.signs = gc["signs"].data_ptr()
     if pending is not None:
-        seq.new_k, seq.new_v = ptr(pending[0]), ptr(pending[1])
+        seq.new_k, seq.new_v = pending[0].data_ptr(), pending[1].data_ptr()
     q2 = q_rope.reshape(n_q, hd)
     if not q2.is_contiguous():
         q2 = q2.contiguous()
     if out is None:
         out = (torch.empty(n_q, _lib.PART_STRIDE, dtype=torch.float32, device=dev) if partial_out
                else torch.empty(n_q, hd, dtype=torch.float16, device=dev))
-    seq.q, seq.out = ptr(q2), ptr(out)
-    seq.phase = ptr(_phase_for(cache, gc, pos_q, t0, t1, dev)) if t1 > t0 else None
-    shape = ops.make_shape(n_q, nkv, gc["k_rank_kernel"], n_comp, t0, t1, n_sink, n_win, n_stream, pos_q,
-                           partial_out, append=pending is not None)
-    need = ops.decode_workspace_bytes(shape, 1)
+    elif not out.is_contiguous() or out.numel() != n_q * (_lib.PART_STRIDE if partial_out else hd):
+        raise _lib.ShardError("out must be a contiguous (n_q, 128) fp16 or (n_q, 132) fp32 tensor")
+    seq.q, seq.out = q2.data_ptr(), out.data_ptr()
+    seq.phase = _phase_for(cache, gc, pos_q, t0, t1, dev).data_ptr() if t1 > t0 else None
+    shape.n_stream, shape.pos_q, shape.append = n_stream, int(pos_q), int(pending is not None)
+    need = ls.need
+    if t1 == t0:                                       # rows only: scratch grows with the rows
+        need = ops.decode_workspace_bytes(shape, 1)
     ws = cache._decode_ws
     if ws is None or ws.numel() < need or ws.device != dev:
         # zero-filled: the header's status word and arrival counters must start at zero
         ws = cache._decode_ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dev)
-    cb = get_codebook(hd, 8, dev) if n_stream > 0 else None
-    ops.decode_attn(seq, 1, shape, cache._inv_freq(dev), cb, ws)
+    ops.decode_attn(seq, 1, shape, ls.inv_ptr, ls.cb_ptr if n_stream > 0 else None, ws)
     return out
 
 
-def fused_attention_compressed(q_rope, layer, pos_q, inv_freq=None, attn_mask=None):
+def fused_attention_compressed(q_rope, layer, pos_q, inv_freq=None, attn_mask=None, out=None):
     """Attention of one query token over the layer's compressed cache; returns
     (1, n_q, 1, hd) in q's dtype, or None if the layer is not compressed.
 
     `attn_mask` is accepted for signature compatibility: for a single trailing
     query of one sequence the causal mask is identically zero (the reference's own
     fused variant skips it for the same reason, src/shard/attention.py:254).
-    `inv_freq` is taken from the cache the layer belongs to.
+    `inv_freq` is taken from the cache the layer belongs to.  `out` (not in the reference's
+    signature) lets the caller name a contiguous (1, n_q, 1, hd) fp16 tensor to write into.
     """
     gc = getattr(layer, "_gpu_compressed", None)
     if gc is None:
         return None
     if "decode_k" in gc:
         return None
-    out = decode_layer(q_rope, layer, pos_q)
+    out = decode_layer(q_rope, layer, pos_q, out=None if out is None else out.view(q_rope.shape[1], q_rope.shape[3]))
     return out.view(1, q_rope.shape[1], 1, q_rope.shape[3])
 
 

@@ -181,15 +181,18 @@ def decode_workspace_bytes(shape, batch=1):
 
 def decode_attn(seq_or_table, batch, shape, inv_freq, codebook, workspace):
     """Launch the fused decode.  `seq_or_table` is a ShardSeq (batch 1) or a uint8 CUDA tensor
-    holding `batch` ShardSeq records."""
+    holding `batch` ShardSeq records; `inv_freq` / `codebook` are tensors or raw device pointers."""
     lib = _lib.load()
     if batch == 1:
         seq_ptr = C.addressof(seq_or_table)
     else:
         seq_ptr = seq_or_table.data_ptr()
-    check(lib.shard_b200_decode_attn(seq_ptr, batch, C.byref(shape), ptr(inv_freq), ptr(codebook),
-                                     ptr(workspace), workspace.numel() * workspace.element_size(),
-                                     cur_stream()), "decode_attn")
+    inv = inv_freq if isinstance(inv_freq, int) else ptr(inv_freq)
+    cb = codebook if isinstance(codebook, int) else ptr(codebook)
+    rc = lib.shard_b200_decode_attn(seq_ptr, batch, C.byref(shape), inv, cb, workspace.data_ptr(),
+                                    workspace.numel() * workspace.element_size(), cur_stream())
+    if rc:
+        check(rc, "decode_attn")
 
 
 def lse_merge(parts, out=None):
