@@ -108,7 +108,8 @@ size_t shard_b200_wprep_bytes(int32_t nkv, int32_t rank);
 
 /*
  * Folds k_coeff_scale into k_basis_f16, appends k_mean as one extra contraction
- * column and lays the result out in tensor-core fragment order.  Runs once per
+ * column and lays the result out as the 128-byte-swizzled K-major operand that
+ * tcgen05.mma reads from shared memory.  Runs once per
  * layer after compression; replaces the per-step operand build of
  * compressed_scores (src/shard/attention.py:34-63).
  * basis_f16: [nkv*128][rank], coeff_scale: [rank], mean_f16: [nkv*128] (all fp16).
@@ -135,15 +136,22 @@ size_t shard_b200_decode_workspace_bytes(const ShardDecodeShape* shape_host, int
  * batch  > 1: `seqs` is a DEVICE pointer to `batch` ShardSeq records describing
  *             independent sequences that share `shape`.
  * inv_freq: [64] fp32.  workspace: at least shard_b200_decode_workspace_bytes(shape, batch)
- * bytes, 16-byte aligned; its contents need not be initialised and are overwritten.
+ * bytes, 16-byte aligned, zero-filled once after it was allocated (see below).
+ * The call is one kernel launch: append (if asked for), attention over all four segments
+ * and the combine of the split-KV partial results.
  * With shape.partial_out the result is the unnormalised per-head triple
  * (max, sum-exp, acc[128]) in standard V space, ready for shard_b200_lse_merge.
  * With shape.append the call also does the work of shard_b200_stream_quantize for the newest
  * token: new_k/new_v are quantised into stream row n_stream-1 (n_stream counts that token)
  * before the stream is attended to.
- * The first 16 bytes of the workspace (status word and a ticket counter) must be zero before
- * the first call that uses a workspace; every call leaves them zero again unless a bounded
- * wait inside the kernel gave up, in which case the status word is left at 1.
+ * The head of the workspace (a status word, then one arrival counter per sequence and KV head:
+ * 16 + 4*batch*nkv bytes rounded up to 16) must be zero before the first call that uses the
+ * workspace; every call leaves it zero again unless a bounded wait inside the kernel gave up,
+ * in which case the status word is left at 1 and the output of that call is undefined.
+ * The kernel is launched with programmatic stream serialization: when the work in front of it
+ * in the stream is another decode call it may start fetching k_coeffs, k_wprep, v_indices and
+ * v_centroids before that call has finished (no decode call writes them); everything else is
+ * read and written only after the preceding work has completed.
  */
 int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const ShardDecodeShape* shape_host,
                            const float* inv_freq, const float* codebook, void* workspace,
@@ -167,8 +175,9 @@ int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const ShardDecod
  *
  *   - Shapes whose split-KV records do not fit in SHARD_B200_STATIC_SCRATCH_BYTES are
  *     refused with SHARD_E_TOO_LARGE and nothing is launched.  With 32 query heads the
- *     area holds 124 records per head: a middle segment of any length (at most 37 chunks)
- *     plus the sink/window record plus about 2,700 streamed tokens.
+ *     area holds 124 records per head; a launch writes at most 36 (18 chunks of the middle
+ *     segment, each with one record for the middle and one for its share of the sink /
+ *     window / streamed rows), so only very wide head counts are refused.
  *   - No cudaMalloc / cudaFree or other allocating call is made, now or later.
  *   - The first call on a device looks up the device address of the built-in area
  *     (cudaGetSymbolAddress, with that device current) and remembers it; make that
