@@ -75,6 +75,28 @@ __device__ __forceinline__ int lloyd_max_code(float v, const float* __restrict__
   return dl < dr ? left : idx;
 }
 
+// The same for four values at once against a 256-entry codebook: a fixed eight-step search
+// (lo = number of entries below v, capped at 255) whose four chains of dependent loads run
+// side by side instead of one after the other.
+__device__ __forceinline__ uint32_t lloyd_max_code4_256(const float (&v)[4], const float* __restrict__ cb) {
+  int lo[4] = {0, 0, 0, 0};
+#pragma unroll
+  for (int step = 128; step >= 1; step >>= 1) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (cb[lo[i] + step - 1] < v[i]) lo[i] += step;
+  }
+  uint32_t packed = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int idx = lo[i], left = idx > 0 ? idx - 1 : 0;
+    const float dl = fabsf(__fsub_rn(cb[left], v[i]));
+    const float dr = fabsf(__fsub_rn(cb[idx], v[i]));
+    packed |= (uint32_t)(dl < dr ? left : idx) << (8 * i);
+  }
+  return packed;
+}
+
 // 8-bit Lloyd-Max code of one 128-channel fp16 vector, one warp per vector (lane l owns
 // channels 4l..4l+3): exact fp64 norm, IEEE division, butterfly in stage order, nearest
 // codebook entry with ties to the right.  Writes 128 codes and the fp16 norm.
@@ -97,13 +119,10 @@ __device__ __forceinline__ void quantize_vec_warp(const __half* __restrict__ src
 #pragma unroll
   for (int i = 0; i < 4; ++i) x[i] = __fmul_rn(__fdiv_rn(x[i], n), sgn[i]);
   fwht128_lane4(x, lane);
-  uint32_t packed = 0;
+  float r[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float r = __fdiv_rn(x[i], SQRT_HD);
-    packed |= (uint32_t)lloyd_max_code(r, cb, 256) << (8 * i);
-  }
-  *reinterpret_cast<uint32_t*>(idx_out + 4 * lane) = packed;
+  for (int i = 0; i < 4; ++i) r[i] = __fdiv_rn(x[i], SQRT_HD);
+  *reinterpret_cast<uint32_t*>(idx_out + 4 * lane) = lloyd_max_code4_256(r, cb);
   if (lane == 0) *norm_out = __float2half_rn(n);
 }
 

@@ -49,7 +49,8 @@ constexpr int PP_MISC_BYTES = 1024 + 1024;   // state + barriers, and slack for 
 __host__ __device__ constexpr int pp_w_bytes(int nw) { return ((32 * nw + 16 + 63) / 64) * 16384; }
 // staging filled by the bulk copy engine: two tiles of packed coefficients (128 rows x R/2 bytes)
 // and one tile of V codes (128 rows x 32 bytes) per consumer group
-__host__ __device__ constexpr int pp_c_bytes(int nw) { return 128 * 16 * nw; }
+// (at least 4224 bytes each, so that the pair can double as the 8.3 KB row-merge scratch)
+__host__ __device__ constexpr int pp_c_bytes(int nw) { return 128 * 16 * nw < 4224 ? 4224 : 128 * 16 * nw; }
 constexpr int PP_VC_BYTES = 128 * VQ_GROUPS;
 __host__ __device__ constexpr int pp_smem_bytes(int nw) {
   return pp_w_bytes(nw) + PP_STAGES * (PP_V_BYTES + PP_P_BYTES) + PP_Q_BYTES + PP_CB_BYTES + PP_ROWQ_BYTES +
@@ -123,7 +124,8 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   float* l_s = misc + 96;                                          // [3][16]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 144);
   volatile int* abort_s = reinterpret_cast<volatile int*>(misc + 145);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(misc + 148);        // 20 mbarriers
+  volatile int* c_cnt = reinterpret_cast<volatile int*>(misc + 146);   // [2] coefficient tiles requested per buffer
+  uint64_t* bars = reinterpret_cast<uint64_t*>(misc + 148);        // 25 mbarriers
 
   const ShardSeq& sq = p.table ? p.table[blockIdx.z] : p.one;
   const ShardDecodeShape& sh = p.sh;
@@ -178,10 +180,12 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   auto S_FULL = [&](int s) { return bar0 + 8u * (uint32_t)(3 + s); };     // MMA2 done
   auto O_FULL = [&](int s) { return bar0 + 8u * (uint32_t)(6 + s); };     // MMA3 done
   auto T_EMPTY = [&](int s) { return bar0 + 8u * (uint32_t)(9 + s); };    // consumers have drained the stage
-  const uint32_t A_EMPTY = bar0 + 8u * 12u;                               // MMA1 has read the A slot
-  const uint32_t W_FULL = bar0 + 8u * 13u;                                // weights have landed
-  auto C_FULL = [&](int b) { return bar0 + 8u * (uint32_t)(14 + b); };    // coefficient tile has landed
-  auto V_FULL = [&](int g) { return bar0 + 8u * (uint32_t)(16 + g); };    // V code tile has landed
+  auto A_EMPTY = [&](int j) { return bar0 + 8u * (uint32_t)(12 + j); };   // MMA1 has read third j of the A slot
+  auto A_FULL = [&](int g) { return bar0 + 8u * (uint32_t)(21 + g); };    // the A operand of group g's next tile is in place
+  const uint32_t APPEND_DONE = bar0 + 8u * 24u;                           // the newest streamed row has been written
+  const uint32_t W_FULL = bar0 + 8u * 15u;                                // weights have landed
+  auto C_FULL = [&](int b) { return bar0 + 8u * (uint32_t)(16 + b); };    // coefficient tile has landed
+  auto V_FULL = [&](int g) { return bar0 + 8u * (uint32_t)(18 + g); };    // V code tile has landed
 
   // tiles of this chunk: evenly spread, the first `tiles_rem` chunks get one more
   const int tile_lo = part * p.tiles_per_chunk + min(part, p.tiles_rem);
@@ -209,9 +213,10 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     if (tid == 0) {
       for (int s = 0; s < PP_STAGES; ++s) {
         mbar_init(KN_FULL(s), 1); mbar_init(S_FULL(s), 1); mbar_init(O_FULL(s), 1); mbar_init(T_EMPTY(s), 4);
-        mbar_init(V_FULL(s), 1);
+        mbar_init(V_FULL(s), 1); mbar_init(A_EMPTY(s), 1); mbar_init(A_FULL(s), 4);
       }
-      mbar_init(A_EMPTY, 1); mbar_init(W_FULL, 1); mbar_init(C_FULL(0), 1); mbar_init(C_FULL(1), 1);
+      mbar_init(W_FULL, 1); mbar_init(C_FULL(0), 1); mbar_init(C_FULL(1), 1); mbar_init(APPEND_DONE, 2);
+      c_cnt[0] = n_my > 0 ? 1 : 0; c_cnt[1] = n_my > 1 ? 1 : 0;
       *abort_s = 0;
       fence_mbar_init();
       // everything the copy engine can fetch ahead: the weights, two coefficient tiles, and the
@@ -256,8 +261,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       qr_s[h * HD + d] = __half2float(x);
     }
   }
-  // fused append by two otherwise idle warps; the barrier below orders it before the reads
-  if (append_here && (warp == 14 || warp == 15)) append_new_token(sq, sh, kv, cbs_s, warp == 15, lane);
+
   if (warp == PP_UNPACK_WARP0) {
     tmem_alloc(smem_u32(tmem_slot), PP_TMEM_COLS);
     tmem_relinquish();
@@ -297,29 +301,51 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     const uint4* phase_tab = reinterpret_cast<const uint4*>(sq.phase);
     const uint4* vc_row = reinterpret_cast<const uint4*>(vc_s + g * PP_VC_BYTES + m * VQ_GROUPS);
     int vc_issued = g < n_my ? 1 : 0;        // V code tiles requested for this group so far
-
-    if (p.n_row_parts > 0) {
-      // This CTA's share of the fp16 / streamed rows (row u belongs to CTA u % n_row_parts), one
-      // warp per row, while the first tile is still on its way.  The twelve warps' states are
-      // merged through group 0's V tile, which nothing has written yet, into a record of its own
-      // (standard V space; the middle's record is in rotated space).
-      SoftmaxState st;
-      softmax_init(st);
-      process_rows(st, sq, sh, kv, part + p.n_row_parts * warp, p.n_row_parts * PP_CONS_WARPS, qr_s, cbs_s, lane);
-      float* scratch = reinterpret_cast<float*>(v_s);
-      partial_store<PP_CONS_WARPS>(st, scratch, warp, lane);
-      named_bar_sync(5, PP_CONS_WARPS * 32);
-      if (g == 0) {
-        partial_merge<PP_CONS_WARPS>(scratch, rec_rows, m);
-        named_bar_sync(1, 128);                       // all of group 0 has read the scratch before any of it gathers
+    const bool issuer = quad == issuer_quad && lane == 0;
+    // MMA1 of tile `it` (one of this group's tiles), issued by the group's issuing thread as soon as
+    // the unpack warps have the A operand in place and the group has drained its stage.  The A slot
+    // is handed back to the unpack warps third by third while the later k-steps still run.
+    constexpr uint32_t IDESC1 = umma_idesc(128, 128, false, false);
+    constexpr int NSUB = (NW + 1) / 2;       // thirds of the A slot: 4 k-steps (64 ranks) each
+    const uint64_t wdesc = smem_desc_sw128(smem_u32(w_s), 16, 1024);
+    auto issue_mma1 = [&](int it) -> bool {
+      const int use = it / PP_STAGES;
+      if (!mbar_wait(A_FULL(g), (uint32_t)(use & 1), abort_s)) return false;
+      if (it + 2 < n_my) { issue_coef(it + 2); c_cnt[it & 1] = c_cnt[it & 1] + 1; }   // the unpack warps are done with that buffer
+      if (it == 0 && !mbar_wait(W_FULL, 0u, abort_s)) return false;
+      if (use > 0 && !mbar_wait(T_EMPTY(g), (uint32_t)((use - 1) & 1), abort_s)) return false;
+      tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        umma_ts_1t(T_g, tmem_base + PP_COL_A + 8 * ks, wdesc + (uint64_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4),
+                   IDESC1, ks > 0 ? 1u : 0u);
+        if ((ks & 3) == 3 && ks / 4 < NSUB - 1) umma_commit_1t(A_EMPTY(ks / 4));
       }
-    }
+      umma_commit_1t(A_EMPTY(NSUB - 1));
+      umma_commit_1t(KN_FULL(g));
+      return true;
+    };
+
+#ifdef SHARD_TC_DEBUG
+    if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 40] = clock64() - pp_kstart__;
+#endif
     PP_T0(0);
 #ifdef SHARD_TC_DEBUG
     if (warp != 0) pp_rec__ = nullptr;
+    if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 41] = clock64() - pp_kstart__;
 #endif
 
     bool bad = false;
+    if (issuer && g < n_my) bad |= !issue_mma1(g);
+    __syncwarp();
+    // Fused append: in the CTA that owns the newest streamed row, two warps of the last consumer
+    // group -- whose first tile is the furthest away -- quantise the new token now.  The row is
+    // read near the end of the kernel by the unpack warps, which wait on APPEND_DONE first.
+    if (append_here && g == PP_STAGES - 1 && quad < 2) {
+      append_new_token(sq, sh, kv, cbs_s, quad == 1, lane);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(APPEND_DONE);
+    }
     for (int it = g; it < n_my; it += PP_STAGES) {
       const uint32_t par = (uint32_t)((it / PP_STAGES) & 1);
       const int t0 = sh.tok_begin + (tile_lo + it) * 128;
@@ -457,15 +483,19 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(T_EMPTY(g));
+      if (issuer && it + PP_STAGES < n_my) bad |= !issue_mma1(it + PP_STAGES);
+      __syncwarp();
       PP_T(7);
     }
     // giving up: do not leave while a copy this thread asked for may still be landing
-    if (bad && quad == issuer_quad && lane == 0 && vc_issued > 0)
+#ifdef SHARD_TC_DEBUG
+    if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 42] = clock64() - pp_kstart__;
+#endif
+    if ((bad || *abort_s) && issuer && vc_issued > 0)
       mbar_wait(V_FULL(g), (uint32_t)((vc_issued - 1) & 1), abort_s);
   } else {
-    // =============================== unpack warps (+ MMA1 issue) =========================
-    constexpr uint32_t IDESC1 = umma_idesc(128, 128, false, false);
-    const uint64_t wdesc = smem_desc_sw128(smem_u32(w_s), 16, 1024);
+    // =============================== unpack warps =========================================
+    constexpr int NSUB = (NW + 1) / 2;
     const int quad = warp - PP_UNPACK_WARP0, m = quad * 32 + lane;
     const uint32_t lane_A = tmem_base + PP_COL_A + ((uint32_t)(quad * 32) << 16);
     {
@@ -473,63 +503,63 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       const uint32_t ones[8] = {0x00003C00u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
       tmem_st_x8(lane_A + R / 2, ones);
     }
-    int c_issued = min(2, n_my);             // coefficient tiles requested so far (thread 0 asked for the first two)
     PP_T0(1);
 #ifdef SHARD_TC_DEBUG
     if (warp != PP_UNPACK_WARP0) pp_rec__ = nullptr;
 #endif
     bool bad = false;
-    for (int it = 0; it < n_my; ++it) {
-      bad |= !mbar_wait(C_FULL(it & 1), (uint32_t)((it >> 1) & 1), abort_s);
-      if (it > 0) {
-        bad |= !mbar_wait(A_EMPTY, (uint32_t)((it - 1) & 1), abort_s);
-        tc_fence_after();
-      }
-      PP_T(0);
+    for (int it = 0; it < n_my && !bad; ++it) {
+      bad = !mbar_wait(C_FULL(it & 1), (uint32_t)((it >> 1) & 1), abort_s);
       const uint4* row = reinterpret_cast<const uint4*>(c_s + (it & 1) * pp_c_bytes(NW) + m * (R / 2));
 #pragma unroll
-      for (int i = 0; i < NW; ++i) {
-        const uint4 xi = row[i];
-        const uint32_t wv[4] = {xi.x, xi.y, xi.z, xi.w};
-        uint32_t o[16];
+      for (int j = 0; j < NSUB; ++j) {
+        // third j of the slot is free once the previous tile's MMA1 has run its k-steps over it
+        if (it > 0) bad |= !mbar_wait(A_EMPTY(j), (uint32_t)((it - 1) & 1), abort_s);
+        bad = __any_sync(0xffffffffu, bad || *abort_s);
+        if (bad) break;                                 // uniform over the warp
+        tc_fence_after();
+        PP_T(0);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const uint32_t hi = wv[e] >> 8;
-          o[4 * e + 0] = nib2half2_tc(wv[e]);          // ranks 8c+0, 8c+4 of word c = 4i+e
-          o[4 * e + 1] = nib2half2_hi(wv[e]);          //       8c+1, 8c+5
-          o[4 * e + 2] = nib2half2_tc(hi);             //       8c+2, 8c+6
-          o[4 * e + 3] = nib2half2_hi(hi);             //       8c+3, 8c+7
+        for (int i = 2 * j; i < 2 * j + 2 && i < NW; ++i) {
+          const uint4 xi = row[i];
+          const uint32_t wv[4] = {xi.x, xi.y, xi.z, xi.w};
+          uint32_t o[16];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t hi = wv[e] >> 8;
+            o[4 * e + 0] = nib2half2_tc(wv[e]);          // ranks 8c+0, 8c+4 of word c = 4i+e
+            o[4 * e + 1] = nib2half2_hi(wv[e]);          //       8c+1, 8c+5
+            o[4 * e + 2] = nib2half2_tc(hi);             //       8c+2, 8c+6
+            o[4 * e + 3] = nib2half2_hi(hi);             //       8c+3, 8c+7
+          }
+          tmem_st_x16(lane_A + 16 * i, o);
         }
-        tmem_st_x16(lane_A + 16 * i, o);
+        PP_T(1);
       }
+      if (bad) break;
       tmem_wait_st();
       tc_fence_before();
-      bad = named_bar_or(4, 128, bad || *abort_s);
-      if (bad) break;                                   // uniform over the four unpack warps
-      PP_T(1);
-      if (quad == 0) {
-        if (lane == 0) {
-          if (it + 2 < n_my) { issue_coef(it + 2); ++c_issued; }   // all four warps have read the buffer
-          const int s = it % PP_STAGES, use = it / PP_STAGES;
-          if (it == 0) mbar_wait(W_FULL, 0u, abort_s);
-          if (use > 0) mbar_wait(T_EMPTY(s), (uint32_t)((use - 1) & 1), abort_s);
-          tc_fence_after();
-          const uint32_t T = tmem_base + 128u * (uint32_t)s;
-#pragma unroll
-          for (int ks = 0; ks < KSTEPS; ++ks)
-            umma_ts_1t(T, tmem_base + PP_COL_A + 8 * ks, wdesc + (uint64_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4),
-                       IDESC1, ks > 0 ? 1u : 0u);
-          umma_commit_1t(KN_FULL(s));
-          umma_commit_1t(A_EMPTY);
-        }
-        __syncwarp();
-        PP_T(2);
-      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(A_FULL(it % PP_STAGES));   // this warp's rows are in place, its reads of c_s done
+      PP_T(2);
     }
-    // giving up: do not leave while a copy this thread asked for may still be landing
-    if (bad && quad == 0 && lane == 0) {
-      mbar_wait(W_FULL, 0u, abort_s);
-      for (int j = max(0, c_issued - 2); j < c_issued; ++j) mbar_wait(C_FULL(j & 1), (uint32_t)((j >> 1) & 1), abort_s);
+    // The unpack warps run about three tiles ahead of the consumers.  In that slack they take this
+    // CTA's share of the fp16 / streamed rows (row u belongs to CTA u % n_row_parts), one warp per
+    // row.  The rows get a record of their own: standard V space, while the middle's record is in rotated space.
+    // The coefficient staging buffers are free by now and serve as merge scratch.
+    bad = named_bar_or(4, 128, bad || *abort_s);
+    PP_T(3);
+    if (!bad && p.n_row_parts > 0) {
+      if (append_here) bad = !mbar_wait(APPEND_DONE, 0u, abort_s);
+      PP_T(4);
+      SoftmaxState st;
+      softmax_init(st);
+      process_rows(st, sq, sh, kv, part + p.n_row_parts * quad, p.n_row_parts * 4, qr_s, cbs_s, lane);
+      float* scratch = reinterpret_cast<float*>(c_s);
+      partial_store<4>(st, scratch, quad, lane);
+      named_bar_sync(4, 128);
+      partial_merge<4>(scratch, rec_rows, m);
+      PP_T(5);
     }
   }
 
@@ -547,33 +577,38 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     for (int j = 0; j < 16; ++j) acc_s[(16 * g + j) * HD + m] = acc[j];
   }
   __syncthreads();
-  if (tid < 256) {
-    const int half = tid >> 7, m = tid & 127;
+  {
+    const int h = tid >> 7, m = tid & 127;              // 512 threads: one (head, channel) each
     const float ch = __half2float(reinterpret_cast<const __half*>(sq.v_ch)[kv * HD + m]);
+    float M = neg_inf();
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      const int h = 2 * half + hh;
-      float M = neg_inf();
+    for (int e = 0; e < 12; ++e) M = fmaxf(M, m_s[16 * (e >> 2) + 4 * (e & 3) + h]);
+    float L = 0.f, a = 0.f;
 #pragma unroll
-      for (int e = 0; e < 12; ++e) M = fmaxf(M, m_s[16 * (e >> 2) + 4 * (e & 3) + h]);
-      float L = 0.f, a = 0.f;
-#pragma unroll
-      for (int e = 0; e < 12; ++e) {
-        const int idx = 16 * (e >> 2) + 4 * (e & 3) + h;
-        const float mv = m_s[idx];
-        const float wt = (mv == neg_inf()) ? 0.f : exp2f((mv - M) * LOG2E);
-        L = fmaf(wt, l_s[idx], L);
-        a = fmaf(wt, acc_s[idx * HD + m], a);
-      }
-      float* rec = rec_base + h * PART;
-      if (m == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
-      rec[4 + m] = a * ch;
+    for (int e = 0; e < 12; ++e) {
+      const int idx = 16 * (e >> 2) + 4 * (e & 3) + h;
+      const float mv = m_s[idx];
+      const float wt = (mv == neg_inf()) ? 0.f : exp2f((mv - M) * LOG2E);
+      L = fmaf(wt, l_s[idx], L);
+      a = fmaf(wt, acc_s[idx * HD + m], a);
     }
+    float* rec = rec_base + h * PART;
+    if (m == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
+    rec[4 + m] = a * ch;
   }
-  if (tid == 0 && *abort_s && p.status) atomicExch(p.status, 1);
+  if (tid == 0 && *abort_s) {
+    // gave up somewhere: do not leave while a bulk copy may still be landing in this CTA's memory
+    mbar_wait(W_FULL, 0u, abort_s);
+    for (int b = 0; b < 2; ++b)
+      if (c_cnt[b] > 0) mbar_wait(C_FULL(b), (uint32_t)((c_cnt[b] - 1) & 1), abort_s);
+    if (p.status) atomicExch(p.status, 1);
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == PP_UNPACK_WARP0) tmem_dealloc(tmem_base, PP_TMEM_COLS);
+#ifdef SHARD_TC_DEBUG
+  if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 43] = clock64() - pp_kstart__;
+#endif
   ticket_combine<PP_THREADS>(p, sq, kv, blockIdx.z, reinterpret_cast<float*>(w_s), tid);
 #ifdef SHARD_TC_DEBUG
   if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 49] += clock64() - pp_kstart__;
