@@ -208,63 +208,72 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
              V_FULL(g));
   };
 
-  // ---- one-time setup -------------------------------------------------------------------
-  {
-    if (tid == 0) {
-      for (int s = 0; s < PP_STAGES; ++s) {
-        mbar_init(KN_FULL(s), 1); mbar_init(S_FULL(s), 1); mbar_init(O_FULL(s), 1); mbar_init(T_EMPTY(s), 4);
-        mbar_init(V_FULL(s), 1); mbar_init(A_EMPTY(s), 1); mbar_init(A_FULL(s), 4);
-      }
-      mbar_init(W_FULL, 1); mbar_init(C_FULL(0), 1); mbar_init(C_FULL(1), 1); mbar_init(APPEND_DONE, 2);
-      c_cnt[0] = n_my > 0 ? 1 : 0; c_cnt[1] = n_my > 1 ? 1 : 0;
-      *abort_s = 0;
-      fence_mbar_init();
-      // everything the copy engine can fetch ahead: the weights, two coefficient tiles, and the
-      // first V code tile of every consumer group
-      mbar_expect_tx(W_FULL, (uint32_t)W_BYTES);
-      bulk_g2s(smem_u32(w_s), reinterpret_cast<const unsigned char*>(sq.k_wprep) + (size_t)kv * W_BYTES,
-               (uint32_t)W_BYTES, W_FULL);
-      for (int j = 0; j < min(2, n_my); ++j) issue_coef(j);
-      for (int j = 0; j < min(PP_STAGES, n_my); ++j) issue_vcodes(j);
-    }
-    if (tid < 256) cbv[tid] = reinterpret_cast<const uint2*>(sq.v_centroids)[tid];
-    else if (sh.n_stream > 0) cbs_s[tid - 256] = p.codebook[tid - 256];
-    uint4* z = reinterpret_cast<uint4*>(p_s);
-    for (int i = tid; i < (PP_STAGES * PP_P_BYTES + PP_Q_BYTES) / 16; i += PP_THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
-#ifdef SHARD_TC_DEBUG
-    if (tid < 48) reinterpret_cast<long long*>(smem + pp_smem_bytes(NW) - 1024 - 512)[tid] = 0;
-#endif
+  // ---- one-time setup: every warp does its share, one CTA barrier at the end ---------------------
+  if (warp == PP_UNPACK_WARP0) {
+    tmem_alloc(smem_u32(tmem_slot), PP_TMEM_COLS);
+    tmem_relinquish();
   }
+  if (tid == 0) {
+    // first the barriers of the bulk copies, so that the copy engine starts as early as possible:
+    // the weights, two coefficient tiles, and the first V code tile of every consumer group
+    mbar_init(C_FULL(0), 1); mbar_init(C_FULL(1), 1); mbar_init(W_FULL, 1);
+    for (int g = 0; g < PP_STAGES; ++g) mbar_init(V_FULL(g), 1);
+    c_cnt[0] = n_my > 0 ? 1 : 0; c_cnt[1] = n_my > 1 ? 1 : 0;
+    fence_mbar_init();
+    if (n_my > 0) issue_coef(0);
+    mbar_expect_tx(W_FULL, (uint32_t)W_BYTES);
+    bulk_g2s(smem_u32(w_s), reinterpret_cast<const unsigned char*>(sq.k_wprep) + (size_t)kv * W_BYTES,
+             (uint32_t)W_BYTES, W_FULL);
+    if (n_my > 1) issue_coef(1);
+    for (int j = 0; j < min(PP_STAGES, n_my); ++j) issue_vcodes(j);
+  } else if (tid == 32) {
+    for (int s = 0; s < PP_STAGES; ++s) {
+      mbar_init(KN_FULL(s), 1); mbar_init(S_FULL(s), 1); mbar_init(O_FULL(s), 1); mbar_init(T_EMPTY(s), 4);
+      mbar_init(A_EMPTY(s), 1); mbar_init(A_FULL(s), 4);
+    }
+    mbar_init(APPEND_DONE, 2);
+    *abort_s = 0;
+    fence_mbar_init();
+  }
+  if (tid >= 256) cbv[tid - 256] = reinterpret_cast<const uint2*>(sq.v_centroids)[tid - 256];
+  else if (tid >= 32 && tid < 128 && sh.n_stream > 0)
+    for (int i = tid - 32; i < 256; i += 96) cbs_s[i] = p.codebook[i];
+  {
+    // P rows that a token's warp does not own stay zero for the whole kernel
+    uint4* z = reinterpret_cast<uint4*>(p_s);
+    for (int i = tid; i < (PP_STAGES * PP_P_BYTES) / 16; i += PP_THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
+  }
+#ifdef SHARD_TC_DEBUG
+  if (tid < 48) reinterpret_cast<long long*>(smem + pp_smem_bytes(NW) - 1024 - 512)[tid] = 0;
+  if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 36] = clock64() - pp_kstart__;
+#endif
   // Up to here only tensors that no decode call ever writes were touched (weights, coefficients,
   // V codes, codebooks).  The query, the new token, the stream rows, the phase table, the scratch
   // and the output may come from, or still be in use by, the call before this one.
   griddep_wait();
-  __syncthreads();
-  if (tid < HD) {
-    // un-rotated query (fp16 arithmetic as the reference) -> Q operand rows 0..3; element of pair i
-    // (c or d part) sits at the contraction position of the in-place K~ layout: column
-    // 8*(i/8) + (i%8)/2 (+4 for the d part), two elements per column
-    const int d = tid, i = d & 63;
+  if (tid >= 128 && tid < 256) {
+    // un-rotated query (fp16 arithmetic as the reference) -> Q operand rows 0..3 (rows 4..15 are
+    // zero); element of pair i (c or d part) sits at the contraction position of the in-place K~
+    // layout: column 8*(i/8) + (i%8)/2 (+4 for the d part), two elements per column
+    const int d = tid - 128, i = d & 63;
     const int kk = 2 * (8 * (i >> 3) + ((i & 7) >> 1) + (d >= 64 ? 4 : 0)) + (i & 1);
     const float phase = __fmul_rn((float)sh.pos_q, p.inv_freq[i]);
     float sn, cs;
     sincosf(phase, &sn, &cs);
     const __half c16 = __float2half_rn(cs), s16 = __float2half_rn(sn);
     const __half* qg = reinterpret_cast<const __half*>(sq.q) + (size_t)kv * GQA * HD;
+    unsigned char* qcol = q_s + (kk >> 6) * 2048 + (kk & 7) * 2;
 #pragma unroll
     for (int h = 0; h < GQA; ++h) {
       const __half x = qg[h * HD + d];
       const __half other = qg[h * HD + (d ^ 64)];
       const __half rot = (d < 64) ? __hneg(other) : other;
       const __half un = __hsub(__hmul(x, c16), __hmul(rot, s16));
-      *reinterpret_cast<__half*>(q_s + (kk >> 6) * 2048 + sw128_off(h, (kk >> 3) & 7) + (kk & 7) * 2) = un;
+      *reinterpret_cast<__half*>(qcol + sw128_off(h, (kk >> 3) & 7)) = un;
       qr_s[h * HD + d] = __half2float(x);
     }
-  }
-
-  if (warp == PP_UNPACK_WARP0) {
-    tmem_alloc(smem_u32(tmem_slot), PP_TMEM_COLS);
-    tmem_relinquish();
+#pragma unroll
+    for (int n = GQA; n < 16; ++n) *reinterpret_cast<__half*>(qcol + sw128_off(n, (kk >> 3) & 7)) = __float2half_rn(0.f);
   }
   fence_proxy_async();
   tc_fence_before();
@@ -336,7 +345,13 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
 #endif
 
     bool bad = false;
+#ifdef SHARD_TC_DEBUG
+    if (g_pp_debug && issuer && g == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 44] = clock64() - pp_kstart__;
+#endif
     if (issuer && g < n_my) bad |= !issue_mma1(g);
+#ifdef SHARD_TC_DEBUG
+    if (g_pp_debug && issuer && g == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 45] = clock64() - pp_kstart__;
+#endif
     __syncwarp();
     // Fused append: in the CTA that owns the newest streamed row, two warps of the last consumer
     // group -- whose first tile is the furthest away -- quantise the new token now.  The row is
@@ -364,6 +379,10 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       bad |= !mbar_wait(KN_FULL(g), par, abort_s);
       tc_fence_after();
       PP_T(1);
+#ifdef SHARD_TC_DEBUG
+      if (g_pp_debug && tid == 0 && it == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 46] = clock64() - pp_kstart__;
+      if (g_pp_debug && tid == 0 && it == 3) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 47] = clock64() - pp_kstart__;
+#endif
 
       // ---- rotate: 8 chunks of 8 pairs; K~ goes back in place --------------------------------
       // chunk ch reads c columns [8ch, 8ch+8) and d columns [64+8ch, ...) and writes 4 columns of c'
