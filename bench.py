@@ -422,6 +422,10 @@ def run_seqsplit(args):
     part = torch.empty(N_Q, 132, dtype=torch.float32, device=dev)
     out = torch.empty(L, N_Q, HD, dtype=torch.float16, device=dev)
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K * L)]
+    peer = None
+    if world > 1 and args.merge == "peer":
+        from shard_b200.parallel import PeerExchange
+        peer = PeerExchange(N_KV)
 
     def barrier():
         if world > 1:
@@ -439,11 +443,14 @@ def run_seqsplit(args):
             if e: e[0].record()
             decode_layer(q_pool[j, li], layer, pos, partial_out=True, with_fp16_segments=first, out=part)
             if e: e[1].record()
-            if world > 1:
-                dist.all_gather_into_tensor(parts.view(-1), part.view(-1))
+            if peer is not None:
+                peer.merge(part, out=out[li])                        # peer stores + flags + merge, one kernel
             else:
-                parts[0].copy_(part)
-            ops.lse_merge(parts, out=out[li])
+                if world > 1:
+                    dist.all_gather_into_tensor(parts.view(-1), part.view(-1))
+                else:
+                    parts[0].copy_(part)
+                ops.lse_merge(parts, out=out[li])
             if e: e[2].record()
         cache._fused_decode_update = False
 
@@ -479,7 +486,9 @@ def run_seqsplit(args):
             "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16", "data": "synthetic",
             "config": {"workload": f"cfg4: one {T}-token sequence, {L} layers, compressed middle split into "
-                                   f"{world} contiguous token range(s) (random codes), log-sum-exp merge over NCCL",
+                                   f"{world} contiguous token range(s) (random codes), log-sum-exp merge "
+                                   + ("over NVLink peer memory inside the merge kernel" if peer is not None
+                                      else "after an NCCL all-gather" if world > 1 else "on one GPU"),
                        "l2": "inputs larger than L2: one step touches %.0f MB of cache per GPU" % (bytes_ls * L / 1e6),
                        "parallelism": f"sequence-split x{world}"},
             "decode_us_per_layer": dec_ms * 1e3 / L, "merge_us_per_layer": mrg_ms * 1e3 / L,
@@ -494,6 +503,9 @@ def run_seqsplit(args):
             "gpu_launches": K * (1 + L * 2), "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
+    if peer is not None:
+        peer.check()
+        peer.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -510,6 +522,9 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4"],
                     help="cfg2: one 32K sequence per GPU (headline); cfg3: 64 x 8K sequences sharded by batch; "
                          "cfg4: one 131072-token sequence split by token range, merged over NCCL")
+    ap.add_argument("--merge", default="peer", choices=["peer", "nccl"],
+                    help="cfg4 at N > 1: exchange the partial records over peer memory inside the merge "
+                         "kernel (default) or with an NCCL all-gather followed by a merge launch")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -199,6 +199,31 @@ int shard_b200_decode_attn_noalloc(const ShardSeq* seq_host, const ShardDecodeSh
 int shard_b200_lse_merge(const float* parts, int32_t n_parts, int32_t n_q, void* out_f16, void* stream);
 
 /*
+ * Sequence-split decode on one multi-GPU node: exchange of the per-rank partial records over
+ * NVLink peer memory and their merge, in one kernel per rank and layer-step (no reference
+ * counterpart; the mixing formula is fused_attention_compressed_full's,
+ * src/shard/attention.py:262-266).
+ *
+ * Every rank allocates one exchange buffer of shard_b200_peer_buffer_bytes(world, nkv) bytes with
+ * shard_b200_peer_alloc (cudaMalloc + zero fill + CUDA IPC export: a set-up call, not for the
+ * hot path), hands the 64-byte handle to the other ranks by any means, and opens theirs with
+ * shard_b200_peer_open.  shard_b200_seqsplit_merge then takes this rank's fp32 [4*nkv][132]
+ * partial (the output of shard_b200_decode_attn with shape.partial_out), stores it into every
+ * rank's buffer with plain peer stores, publishes `epoch`, waits -- bounded, about 0.2 s, after
+ * which *status_dev is set to 1 and out is left unwritten -- for all ranks' records of the same
+ * epoch and merges them in rank order into out_f16 (fp16 [4*nkv][128]), bit-identical on every
+ * rank.  `bufs_host` is a HOST array of `world` device pointers (entry `rank` = own buffer);
+ * `epoch` starts at 1 and grows by 1 per call, in step on all ranks.
+ */
+size_t shard_b200_peer_buffer_bytes(int32_t world, int32_t nkv);
+int shard_b200_peer_alloc(size_t bytes, void** ptr_out, void* handle_out_64);
+int shard_b200_peer_open(const void* handle_64, void** ptr_out);
+int shard_b200_peer_close(void* ptr);
+int shard_b200_peer_free(void* ptr);
+int shard_b200_seqsplit_merge(const float* my_part, void* const* bufs_host, int32_t rank, int32_t world,
+                              int32_t nkv, uint32_t epoch, void* out_f16, int* status_dev, void* stream);
+
+/*
  * 8-bit Lloyd-Max quantisation of one new K and V token per KV head and append
  * at row `slot` of the stream buffers: CacheLayer._stream_append
  * (src/shard/cache.py:193-241) + quantize_per_token (src/shard/streaming.py:59-72).

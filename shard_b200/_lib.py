@@ -46,6 +46,13 @@ _SIGNATURES = {
     "shard_b200_decode_attn_noalloc": (C.c_int, [C.c_void_p, C.POINTER(ShardDecodeShape), C.c_void_p, C.c_void_p,
                                                  C.c_void_p]),
     "shard_b200_lse_merge": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "shard_b200_peer_buffer_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
+    "shard_b200_peer_alloc": (C.c_int, [C.c_size_t, C.c_void_p, C.c_void_p]),
+    "shard_b200_peer_open": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "shard_b200_peer_close": (C.c_int, [C.c_void_p]),
+    "shard_b200_peer_free": (C.c_int, [C.c_void_p]),
+    "shard_b200_seqsplit_merge": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_uint32,
+                                            C.c_void_p, C.c_void_p, C.c_void_p]),
     "shard_b200_stream_quantize": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                              C.c_void_p]),
     "shard_b200_stream_dequant": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,

@@ -1,0 +1,165 @@
+// Sequence-split decode: exchange of the per-rank partial records over NVLink peer memory and
+// their log-sum-exp merge, in one kernel.
+//
+// Every rank owns one exchange buffer (plain cudaMalloc memory, opened by the other ranks of
+// the node through CUDA IPC).  Layout, identical on all ranks:
+//
+//   flags [2 slots][world][nkv] u32      "rank r has delivered its records of epoch e for KV head kv"
+//   parts [2 slots][world][n_q][132] f32 rank r's (max, sum-exp, 0, 0, acc[128]) per query head
+//
+// One launch per layer-step and rank, grid = nkv CTAs (CTA kv handles that KV head's four query
+// heads): (1) store this rank's four records into slot e % 2 of EVERY rank's buffer with plain
+// peer stores, (2) system-scope fence, then publish the epoch number in every rank's flag word,
+// (3) wait -- bounded -- until all `world` flag words of the own buffer show the epoch,
+// (4) merge the `world` records of the own buffer in rank order: same operations and order as
+// decode_combine_kernel, so every rank gets bit-identical output.
+//
+// Two slots suffice: a rank can only be writing epoch e + 2 after every rank has published
+// e + 1, i.e. after every rank has finished reading epoch e (same slot) in stream order.
+// No multicast, no multimem: plain loads and stores on peer pointers.
+#include <cstring>
+
+#include "common.cuh"
+
+namespace shard {
+
+constexpr int PEER_MAX_WORLD = 16;
+constexpr long long PEER_WAIT_SPINS = 4000000;   // x ~50 ns: gives up after roughly 0.2 s
+
+struct PeerParams {
+  unsigned char* bufs[PEER_MAX_WORLD];   // exchange buffer of every rank (own entry = local pointer)
+  const float* my_part;                  // [n_q][132]
+  void* out;                             // fp16 [n_q][128]
+  int* status;                           // set to 1 when the bounded wait gave up (may be null)
+  int rank, world, nkv;
+  unsigned int epoch;
+};
+
+__host__ __device__ inline size_t peer_flag_bytes(int world, int nkv) {
+  return ((size_t)2 * world * nkv * sizeof(unsigned int) + 255) & ~(size_t)255;
+}
+__host__ __device__ inline size_t peer_slot_floats(int world, int nkv) { return (size_t)world * nkv * GQA * PART; }
+
+__global__ void __launch_bounds__(GQA* HD) seqsplit_exchange_merge_kernel(const __grid_constant__ PeerParams p) {
+  __shared__ int timed_out;
+  const int kv = blockIdx.x, tid = threadIdx.x;
+  const int slot = (int)(p.epoch & 1u);
+  const int n_q = p.nkv * GQA;
+  const size_t flag_bytes = peer_flag_bytes(p.world, p.nkv);
+  const size_t slot_floats = peer_slot_floats(p.world, p.nkv);
+  if (tid == 0) timed_out = 0;
+
+  // (1) this rank's four records of KV head kv -> every rank's buffer
+  const float4* src = reinterpret_cast<const float4*>(p.my_part + (size_t)kv * GQA * PART);
+  constexpr int N4 = GQA * PART / 4;   // 132 float4
+  for (int r = 0; r < p.world; ++r) {
+    float* parts = reinterpret_cast<float*>(p.bufs[r] + flag_bytes) + slot * slot_floats;
+    float4* dst = reinterpret_cast<float4*>(parts + ((size_t)p.rank * n_q + (size_t)kv * GQA) * PART);
+    for (int i = tid; i < N4; i += blockDim.x) dst[i] = src[i];
+  }
+  // (2) make the records visible system-wide, then publish the epoch
+  __threadfence_system();
+  __syncthreads();
+  if (tid < p.world) {
+    volatile unsigned int* flag =
+        reinterpret_cast<volatile unsigned int*>(p.bufs[tid]) + ((size_t)slot * p.world + p.rank) * p.nkv + kv;
+    *flag = p.epoch;
+  }
+  // (3) bounded wait for everybody's records of this epoch in the own buffer
+  if (tid < p.world) {
+    volatile unsigned int* flag =
+        reinterpret_cast<volatile unsigned int*>(p.bufs[p.rank]) + ((size_t)slot * p.world + tid) * p.nkv + kv;
+    long long spins = 0;
+    while (*flag != p.epoch) {
+      if (++spins > PEER_WAIT_SPINS) { timed_out = 1; break; }
+      __nanosleep(40);
+    }
+    __threadfence_system();
+  }
+  __syncthreads();
+  if (timed_out) {
+    if (tid == 0 && p.status) atomicExch(p.status, 1);
+    return;
+  }
+  // (4) merge in rank order; all partial records are in standard V space
+  const int h = kv * GQA + (tid >> 7), d = tid & (HD - 1);
+  const float* base = reinterpret_cast<const float*>(p.bufs[p.rank] + flag_bytes) + slot * slot_floats + (size_t)h * PART;
+  const size_t pstride = (size_t)n_q * PART;
+  float M = neg_inf();
+  for (int r = 0; r < p.world; ++r) M = fmaxf(M, __ldcg(base + r * pstride));
+  float L = 0.f, acc = 0.f;
+  for (int r = 0; r < p.world; ++r) {
+    const float* rec = base + r * pstride;
+    const float m = __ldcg(rec);
+    const float wt = (m == neg_inf()) ? 0.f : exp2f((m - M) * LOG2E);
+    L = fmaf(wt, __ldcg(rec + 1), L);
+    acc = fmaf(wt, __ldcg(rec + 4 + d), acc);
+  }
+  reinterpret_cast<__half*>(p.out)[(size_t)h * HD + d] = __float2half_rn(acc / L);
+}
+
+}  // namespace shard
+
+using namespace shard;
+
+extern "C" size_t shard_b200_peer_buffer_bytes(int32_t world, int32_t nkv) {
+  if (world < 1 || world > PEER_MAX_WORLD || nkv < 1) return 0;
+  return peer_flag_bytes(world, nkv) + 2 * peer_slot_floats(world, nkv) * sizeof(float);
+}
+
+extern "C" int shard_b200_peer_alloc(size_t bytes, void** ptr_out, void* handle_out_64) {
+  if (!ptr_out || !handle_out_64 || bytes == 0) return SHARD_E_ARG;
+  void* ptr = nullptr;
+  cudaError_t e = cudaMalloc(&ptr, bytes);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemset(ptr, 0, bytes);
+  if (e != cudaSuccess) { cudaFree(ptr); return (int)e; }
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  e = cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t*>(handle_out_64), ptr);
+  if (e != cudaSuccess) { cudaFree(ptr); return (int)e; }
+  *ptr_out = ptr;
+  return SHARD_OK;
+}
+
+extern "C" int shard_b200_peer_open(const void* handle_64, void** ptr_out) {
+  if (!handle_64 || !ptr_out) return SHARD_E_ARG;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle_64, sizeof(h));
+  cudaError_t e = cudaIpcOpenMemHandle(ptr_out, h, cudaIpcMemLazyEnablePeerAccess);
+  return e == cudaSuccess ? SHARD_OK : (int)e;
+}
+
+extern "C" int shard_b200_peer_close(void* ptr) {
+  if (!ptr) return SHARD_E_ARG;
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  return e == cudaSuccess ? SHARD_OK : (int)e;
+}
+
+extern "C" int shard_b200_peer_free(void* ptr) {
+  if (!ptr) return SHARD_E_ARG;
+  cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? SHARD_OK : (int)e;
+}
+
+extern "C" int shard_b200_seqsplit_merge(const float* my_part, void* const* bufs_host, int32_t rank, int32_t world,
+                                         int32_t nkv, uint32_t epoch, void* out_f16, int* status_dev, void* stream) {
+  if (!my_part || !bufs_host || !out_f16 || world < 1 || world > PEER_MAX_WORLD || rank < 0 || rank >= world ||
+      nkv < 1 || epoch == 0)
+    return SHARD_E_ARG;
+  if ((uintptr_t)my_part & 15) return SHARD_E_ALIGN;
+  PeerParams p{};
+  for (int r = 0; r < world; ++r) {
+    if (!bufs_host[r]) return SHARD_E_ARG;
+    p.bufs[r] = reinterpret_cast<unsigned char*>(bufs_host[r]);
+  }
+  p.my_part = my_part;
+  p.out = out_f16;
+  p.status = status_dev;
+  p.rank = rank;
+  p.world = world;
+  p.nkv = nkv;
+  p.epoch = epoch;
+  seqsplit_exchange_merge_kernel<<<nkv, GQA * HD, 0, (cudaStream_t)stream>>>(p);
+  SHARD_CHECK_LAUNCH();
+  return SHARD_OK;
+}

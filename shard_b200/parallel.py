@@ -88,11 +88,81 @@ def all_gather_partials(part: torch.Tensor, group=None, out: torch.Tensor | None
     return out
 
 
-def seqsplit_decode(q_rope, layer, pos_q, group=None, gather_buf=None, timing=None):
+class PeerExchange:
+    """Exchange buffers of the ranks of one node, opened over CUDA IPC, and the epoch counter of
+    `shard_b200_seqsplit_merge`: the partial records of a sequence-split decode step travel as
+    plain peer stores over NVLink and are merged by the same kernel that sent them, instead of an
+    NCCL all-gather followed by a merge launch.  All ranks must call `merge` the same number of
+    times, in the same order.  Needs every rank on its own GPU of one node with peer access."""
+
+    def __init__(self, nkv: int, group=None, device=None):
+        import ctypes as C
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.nkv = nkv
+        self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        lib = _lib.load()
+        nbytes = lib.shard_b200_peer_buffer_bytes(self.world, nkv)
+        if nbytes == 0:
+            raise _lib.ShardError("unsupported world size for the peer exchange (1..16 ranks)")
+        own = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        with torch.cuda.device(self.dev):
+            _lib.check(lib.shard_b200_peer_alloc(nbytes, C.byref(own), handle), "peer_alloc")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            self._own = own.value
+            self._opened = []
+            ptrs = []
+            for r in range(self.world):
+                if r == self.rank:
+                    ptrs.append(self._own)
+                    continue
+                p = C.c_void_p()
+                hbuf = C.create_string_buffer(handles[r], 64)
+                _lib.check(lib.shard_b200_peer_open(hbuf, C.byref(p)), "peer_open")
+                self._opened.append(p.value)
+                ptrs.append(p.value)
+        self._ptrs = (C.c_void_p * self.world)(*ptrs)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.epoch = 0
+        dist.barrier(group=group)            # every buffer is zeroed and opened before the first store
+
+    def merge(self, part: torch.Tensor, out: torch.Tensor | None = None):
+        """part: this rank's (n_q, 132) fp32 record -> (n_q, 128) fp16 merged over all ranks."""
+        n_q = 4 * self.nkv
+        if out is None:
+            out = torch.empty(n_q, 128, dtype=torch.float16, device=part.device)
+        self.epoch += 1
+        _lib.check(_lib.load().shard_b200_seqsplit_merge(part.data_ptr(), self._ptrs, self.rank, self.world, self.nkv,
+                                                         self.epoch, out.data_ptr(), self.status.data_ptr(),
+                                                         _lib.cur_stream()), "seqsplit_merge")
+        return out
+
+    def check(self):
+        """Raise if a bounded wait inside a merge gave up (synchronises the device)."""
+        if int(self.status.item()) != 0:
+            raise _lib.ShardError("sequence-split merge timed out waiting for a peer's records")
+
+    def close(self):
+        lib = _lib.load()
+        torch.cuda.synchronize(self.dev)
+        dist.barrier(group=self.group)       # nobody is still storing into a buffer that goes away
+        for p in self._opened:
+            lib.shard_b200_peer_close(p)
+        self._opened = []
+        if self._own:
+            lib.shard_b200_peer_free(self._own)
+            self._own = None
+
+
+def seqsplit_decode(q_rope, layer, pos_q, group=None, gather_buf=None, timing=None, peer=None):
     """Sequence-split decode of one layer whose dictionary was cut by `shard_layer_tokens`.
 
     Every rank calls this with the same query; all ranks return the same
-    (1, n_q, 1, hd) fp16 tensor (the combine runs in fixed rank order).
+    (1, n_q, 1, hd) fp16 tensor (the combine runs in fixed rank order).  With `peer`
+    (a `PeerExchange`) the records travel over NVLink peer memory inside the merge kernel;
+    without it through an NCCL all-gather followed by `lse_merge`.
     `timing`, if given, is a dict receiving CUDA events around the merge step.
     """
     from .attention import decode_layer
@@ -100,8 +170,11 @@ def seqsplit_decode(q_rope, layer, pos_q, group=None, gather_buf=None, timing=No
     part = decode_layer(q_rope, layer, pos_q, partial_out=True, with_fp16_segments=(rank == 0))
     if timing is not None:
         timing["merge_start"].record()
-    parts = all_gather_partials(part, group, gather_buf)
-    out = ops.lse_merge(parts)
+    if peer is not None:
+        out = peer.merge(part)
+    else:
+        parts = all_gather_partials(part, group, gather_buf)
+        out = ops.lse_merge(parts)
     if timing is not None:
         timing["merge_end"].record()
     return out.view(1, q_rope.shape[1], 1, q_rope.shape[3])

@@ -1,5 +1,5 @@
 """Two-GPU test of the sequence-split decode: every rank attends to its slice of the compressed
-middle, the per-head (max, sum-exp, acc) records travel through NCCL, and the merged result
+middle, the per-head (max, sum-exp, acc) records travel through NCCL or through peer memory, and the merged result
 equals single-GPU attention over the whole cache.  Skipped on boxes with fewer than 2 GPUs."""
 import os
 import subprocess
@@ -20,7 +20,7 @@ from gpu_helpers import FakeCache, FakeLayer, gc_to_device, random_gc, random_qu
 from oracle import shard_oracle as O
 from conftest import tol_ok
 from shard_b200.cache import attach_kernel_format
-from shard_b200.parallel import seqsplit_decode, shard_layer_tokens
+from shard_b200.parallel import PeerExchange, seqsplit_decode, shard_layer_tokens
 from shard_b200.attention import decode_layer
 
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -44,6 +44,15 @@ assert tol_ok(got, exact, atol=1.5e-3, rtol=5e-3)
 gathered = [None] * world
 dist.all_gather_object(gathered, got.tobytes())
 assert all(x == gathered[0] for x in gathered)      # bitwise identical on every rank
+# the same exchange over NVLink peer memory inside the merge kernel: bit-identical to the NCCL path,
+# also when the two buffer slots are reused over several steps
+peer = PeerExchange(8)
+for step in range(5):
+    out2 = seqsplit_decode(q, mine, 5100, peer=peer)
+    torch.cuda.synchronize()
+    peer.check()
+    assert out2.cpu().numpy()[0, :, 0, :].tobytes() == got.tobytes(), step
+peer.close()
 dist.destroy_process_group()
 print("ok", rank)
 '''
