@@ -1,26 +1,37 @@
-// Split-KV decode pass, warp-specialised and pipelined three tiles deep (tcgen05 + TMEM).
+// One decode step of one layer in one launch: split-KV pass over the compressed middle
+// (tcgen05 + tensor memory + bulk copy engine, warp-specialised, three tiles in flight per SM),
+// the fp16 / streamed rows, the stream append and the combine.
 //
-// One CTA per SM (16 warps) owns one KV head and a run of 128-token tiles of the compressed
-// middle segment.  Three tiles are in flight at any time, each in its own 128-column
-// tensor-memory stage:
+// One CTA per SM (16 warps) owns one KV head and a run of 128-token tiles of the middle segment.
 //
-//   unpack warps (4)    packed int4 coefficients -> fp16 A operand in tensor memory (one A slot,
-//                       recycled as soon as MMA1 of the previous tile has read it); one elected
-//                       thread then issues
-//                       MMA1  K_n[128 tok x 128] = A . W^T           (A from TMEM, W in smem)
-//   consumer groups (3 x 4 warps; group g owns stage g and tiles g, g+3, ...)
-//                       thread = token row: K_n -> + mean -> half2 -> rotate by the relative
-//                       phase -> K~ written in place; expand the token's 32 VQ codes into the
-//                       stage's V tile; one elected thread of the group issues
+//   copy engine         the weights W once; per tile the packed int4 coefficient rows (two buffers,
+//                       two tiles ahead) and the V codes (one buffer per consumer group) land in
+//                       shared memory and are announced on mbarriers -- no load instruction touches
+//                       the cache data
+//   unpack warps (4)    coefficient rows -> fp16 A operand in tensor memory (one A slot, handed back
+//                       by MMA1 in thirds so that the next tile's unpack overlaps its later k-steps);
+//                       in their slack at the end: this CTA's share of the fp16 sink / window rows
+//                       and the streamed rows (dequantised on the fly), as a record of its own
+//   consumer groups (3 x 4 warps; group g owns stage g and tiles g, g+3, ...), thread = token row;
+//                       one thread per group issues all tensor-core work of the group:
+//                       MMA1  K_n[128 tok x 128] = A . W^T           (A from TMEM, W in smem; the last
+//                             k-step adds the mean)
+//                       K_n -> half2 -> rotate by the relative phase -> K~ written in place
 //                       MMA2  S[128 tok x 16]    = K~ . Q^T          (A = K~ from TMEM)
-//                       per-warp online softmax -> P; the elected thread issues
+//                       meanwhile the token's 32 VQ codes are expanded into the group's V tile
+//                       per-warp online softmax -> P
 //                       MMA3  O[128 ch x 16]     = V^T . P^T         (V, P in smem)
 //                       and every thread rescales-and-accumulates its output channel
+//   append              the CTA that owns the newest streamed row quantises the new token in the
+//                       start-up slack of the last consumer group
+//   combine             the last CTA of a (sequence, KV head) to finish merges all records
 //
 // Stage s of tensor memory: columns [128s, 128s+128): un-rotated keys (fp32), overwritten in
-// place by K~ (fp16x2, columns 0-63 of the stage), scores (64-79) and the tile's P.V (80-95).
-// Every hand-over is an mbarrier; every wait is bounded and raises the CTA's abort flag when it
-// gives up, after which all roles drain, tensor memory is freed and the status word is set.
+// place by K~ (fp16x2, columns 0-63 of the stage), scores (64-79) and the tile's P.V (80-95);
+// the A operand sits at [384, 488).
+// Every hand-over is an mbarrier whose waiters see each of its phases; every wait is bounded and
+// raises the CTA's abort flag when it gives up, after which all roles drain, bulk copies in flight
+// are waited for, tensor memory is freed and the status word is set.
 #include <cstdlib>
 
 #include "decode_common.cuh"
@@ -411,6 +422,22 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
         tmem_st_x4(lane_T + 8 * ch + 4, od);
       }
       PP_T(2);
+      tmem_wait_st();
+      PP_T(9);
+      tc_fence_before();
+      bad = named_bar_or(1 + g, 128, bad || *abort_s);
+      if (bad) break;                                   // uniform over the group
+      if (quad == issuer_quad && lane == 0) {
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts_1t(T_g + PP_COL_S, T_g + 8 * ks, qdesc + (uint64_t)(((ks >> 2) * 2048 + (ks & 3) * 32) >> 4), IDESC2,
+                     ks > 0 ? 1u : 0u);
+        umma_commit_1t(S_FULL(g));
+      }
+      __syncwarp();
+      PP_T(3);
+      // (while the tensor core computes the scores)
       // ---- gather the token's V row (32 codes) into the stage's V tile -------------------------
       bad |= !mbar_wait(V_FULL(g), par, abort_s);
       {
@@ -424,24 +451,6 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
         }
       }
       PP_T(8);
-      tmem_wait_st();
-      PP_T(9);
-      fence_proxy_async();
-      PP_T(10);
-      tc_fence_before();
-      bad = named_bar_or(1 + g, 128, bad || *abort_s);
-      if (bad) break;                                   // uniform over the group
-      if (quad == issuer_quad && lane == 0) {
-        if (it + PP_STAGES < n_my) { issue_vcodes(it + PP_STAGES); ++vc_issued; }   // every lane has read its codes
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ts_1t(T_g + PP_COL_S, T_g + 8 * ks, qdesc + (uint64_t)(((ks >> 2) * 2048 + (ks & 3) * 32) >> 4), IDESC2,
-                     ks > 0 ? 1u : 0u);
-        umma_commit_1t(S_FULL(g));
-      }
-      __syncwarp();
-      PP_T(3);
 
       // ---- softmax over this warp's 32 tokens ---------------------------------------------------
       bad |= !mbar_wait(S_FULL(g), par, abort_s);
@@ -472,6 +481,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       bad = named_bar_or(1 + g, 128, bad || *abort_s);
       if (bad) break;                                   // uniform over the group
       if (quad == issuer_quad && lane == 0) {
+        if (it + PP_STAGES < n_my) { issue_vcodes(it + PP_STAGES); ++vc_issued; }   // every lane has read its codes
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
