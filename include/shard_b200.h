@@ -70,6 +70,8 @@ typedef struct ShardSeq {
   void* out;                 /* fp16 [n_q][128] result, or fp32 [n_q][132] partial      */
   const void* new_k;         /* fp16 [nkv][128]   token to append (stream_quantize)     */
   const void* new_v;         /* fp16 [nkv][128]                                         */
+  const void* dec_k;         /* fp16 [nkv][n_dec][128] tokens appended as they are by a */
+  const void* dec_v;         /* non-streaming cache (gc["decode_k"], gc["decode_v"])    */
 } ShardSeq;
 
 /* Scalars shared by every sequence of a launch. */
@@ -86,6 +88,7 @@ typedef struct ShardDecodeShape {
   int32_t pos_q;          /* position of the query token                                 */
   int32_t partial_out;    /* 0: out = fp16 attention; 1: out = fp32 (m, l, acc) partial  */
   int32_t append;         /* 1: first quantise new_k/new_v into stream row n_stream-1 (fused append) */
+  int32_t n_dec;          /* rows of the fp16 decode buffer (dec_k / dec_v)              */
 } ShardDecodeShape;
 
 /*
@@ -125,7 +128,7 @@ size_t shard_b200_decode_workspace_bytes(const ShardDecodeShape* shape_host, int
 
 /*
  * Fused decode attention of one query token over
- * [sink | compressed middle | window | streamed tokens]: replaces
+ * [sink | compressed middle | window | fp16 decode buffer | streamed tokens]: replaces
  * fused_attention_compressed (src/shard/attention.py:270-343) with its callees
  * compressed_scores (18-81), int4_matmul (triton_kernels.py:65-88),
  * _v_weighted_sum_compressed (83-121), vq_weighted_sum_all

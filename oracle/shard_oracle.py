@@ -510,12 +510,17 @@ def vq_decode_rot(gc, nkv=8):
     return (cb[idx].reshape(nkv, n, -1) * ch[:, None, :]).astype(F32)
 
 
-def fused_attention_compressed(q_rope_f16, gc, pos_q, inv_freq, nkv=8, stream=None, attn_mask=None):
-    """Decode attention over [sink | middle | window | stream]; attention.py:270-343.
+def fused_attention_compressed(q_rope_f16, gc, pos_q, inv_freq, nkv=8, stream=None, attn_mask=None,
+                               decode=None):
+    """Decode attention over [sink | middle | window | fp16 decode buffer | stream];
+    attention.py:270-343.
 
     q_rope_f16: (n_q, hd) fp16 (batch 1, one query token).  ``stream`` is an
     optional dict with k_idx, v_idx (s, nkv, hd) u8, k_norm, v_norm (s, nkv)
-    fp16, signs, codebook.  Returns (n_q, hd) fp16.
+    fp16, signs, codebook.  ``decode`` is an optional pair (k, v) of fp16 arrays
+    (nkv, s, hd): the tokens a non-streaming cache appends as they are
+    (gc["decode_k"], gc["decode_v"], attention.py:307-308, 335-338).
+    Returns (n_q, hd) fp16.
     """
     n_q, hd = q_rope_f16.shape
     gqa = n_q // nkv
@@ -532,6 +537,10 @@ def fused_attention_compressed(q_rope_f16, gc, pos_q, inv_freq, nkv=8, stream=No
     parts = [fp16_scores(_h(gc["sink_k"])),
              compressed_scores(q_rope_f16, gc, pos_q, inv_freq, nkv),
              fp16_scores(_h(gc["win_k"]))]
+    n_dec = 0
+    if decode is not None and decode[0].shape[1] > 0:
+        n_dec = decode[0].shape[1]
+        parts.append(fp16_scores(_h(decode[0]), divide=True))
     sk = sv = None
     if stream is not None and stream["k_idx"].shape[0] > 0:
         sk = dequant_stream(stream["k_idx"], stream["k_norm"], stream["signs"], stream["codebook"])
@@ -561,13 +570,16 @@ def fused_attention_compressed(q_rope_f16, gc, pos_q, inv_freq, nkv=8, stream=No
 
     out = (out + pv(w_sink, _h(gc["sink_v"]))).astype(F32)
     out = (out + pv(w_win, _h(gc["win_v"]))).astype(F32)
+    if n_dec:
+        out = (out + pv(w[:, off:off + n_dec], _h(decode[1]))).astype(F32)
+        off += n_dec
     if sv is not None:
         out = (out + pv(w[:, off:off + sv.shape[1]], sv)).astype(F32)
     return out.astype(F16)
 
 
 def attention_exact(q_rope_f16, gc, pos_q, inv_freq, nkv=8, stream=None, tok_range=None,
-                    with_fp16_segments=True):
+                    with_fp16_segments=True, decode=None):
     """Float64 evaluation of the same compressed cache (no fp16 intermediates).
 
     Dequantises K as src/shard/cache.py:92-113 does (but in double), V as
@@ -597,6 +609,9 @@ def attention_exact(q_rope_f16, gc, pos_q, inv_freq, nkv=8, stream=None, tok_ran
     if with_fp16_segments:
         ks = [_h(gc["sink_k"]).astype(np.float64), k_mid, _h(gc["win_k"]).astype(np.float64)]
         vs = [_h(gc["sink_v"]).astype(np.float64), v_mid, _h(gc["win_v"]).astype(np.float64)]
+        if decode is not None and decode[0].shape[1] > 0:
+            ks.append(_h(decode[0]).astype(np.float64))
+            vs.append(_h(decode[1]).astype(np.float64))
         if stream is not None and stream["k_idx"].shape[0] > 0:
             ks.append(dequant_stream(stream["k_idx"], stream["k_norm"], stream["signs"],
                                      stream["codebook"]).astype(np.float64))

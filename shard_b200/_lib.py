@@ -22,14 +22,14 @@ class ShardSeq(C.Structure):
         "k_coeffs", "k_wprep", "v_indices", "v_centroids", "v_ch",
         "sink_k", "sink_v", "win_k", "win_v",
         "st_k_idx", "st_v_idx", "st_k_norm", "st_v_norm",
-        "signs", "phase", "q", "out", "new_k", "new_v")]
+        "signs", "phase", "q", "out", "new_k", "new_v", "dec_k", "dec_v")]
 
 
 class ShardDecodeShape(C.Structure):
     """Mirror of `struct ShardDecodeShape`."""
     _fields_ = [(name, C.c_int32) for name in (
         "n_q", "nkv", "rank", "n_comp", "tok_begin", "tok_end",
-        "n_sink", "n_win", "n_stream", "pos_q", "partial_out", "append")]
+        "n_sink", "n_win", "n_stream", "pos_q", "partial_out", "append", "n_dec")]
 
 
 _SIGNATURES = {

@@ -106,8 +106,6 @@ def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_f
         raise NotImplementedError("decode kernel is built for head_dim 128 and 4 query heads per KV head")
     if q_rope.dtype != torch.float16:
         raise NotImplementedError("fp16 queries only")
-    if "decode_k" in gc:
-        raise NotImplementedError("fp16 decode buffer (non-streaming append) is served by the dequantised path")
     dev = q_rope.device
     t0, t1 = (0, gc["n_compress"]) if tok_range is None else tok_range
     ls = _launch_state(gc, cache, dev, nkv, n_q, t0, t1, with_fp16_segments, partial_out)
@@ -126,6 +124,19 @@ def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_f
             seq.signs = gc["signs"].data_ptr()
     if pending is not None:
         seq.new_k, seq.new_v = pending[0].data_ptr(), pending[1].data_ptr()
+    n_dec = 0
+    if with_fp16_segments and "decode_k" in gc:
+        # tokens a non-streaming cache appends as they are: (1, nkv, s, 128) fp16, re-made by torch.cat
+        # on every step, so the pointers are refreshed on every call
+        dk, dv = gc["decode_k"], gc["decode_v"]
+        if dk.dtype != torch.float16:
+            raise NotImplementedError("fp16 models only")
+        if not dk.is_contiguous():
+            dk = gc["decode_k"] = dk.contiguous()
+        if not dv.is_contiguous():
+            dv = gc["decode_v"] = dv.contiguous()
+        n_dec = dk.shape[2]
+        seq.dec_k, seq.dec_v = dk.data_ptr(), dv.data_ptr()
     q2 = q_rope.reshape(n_q, hd)
     if not q2.is_contiguous():
         q2 = q2.contiguous()
@@ -137,6 +148,7 @@ def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_f
     seq.q, seq.out = q2.data_ptr(), out.data_ptr()
     seq.phase = _phase_for(cache, gc, pos_q, t0, t1, dev).data_ptr() if t1 > t0 else None
     shape.n_stream, shape.pos_q, shape.append = n_stream, int(pos_q), int(pending is not None)
+    shape.n_dec = n_dec
     need = ls.need
     if t1 == t0:                                       # rows only: scratch grows with the rows
         need = ops.decode_workspace_bytes(shape, 1)
@@ -160,8 +172,6 @@ def fused_attention_compressed(q_rope, layer, pos_q, inv_freq=None, attn_mask=No
     """
     gc = getattr(layer, "_gpu_compressed", None)
     if gc is None:
-        return None
-    if "decode_k" in gc:
         return None
     out = decode_layer(q_rope, layer, pos_q, out=None if out is None else out.view(q_rope.shape[1], q_rope.shape[3]))
     return out.view(1, q_rope.shape[1], 1, q_rope.shape[3])

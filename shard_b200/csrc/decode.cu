@@ -53,7 +53,7 @@ static DecodePlan make_plan(const ShardDecodeShape& sh, int batch) {
   }
   // the fp16 / streamed rows ride along in the chunk CTAs (dealt out row by row, handled while a
   // CTA waits for its first tile); only a launch without a middle gets CTAs just for them
-  const int n_rows = sh.n_sink + sh.n_win + sh.n_stream;
+  const int n_rows = sh.n_sink + sh.n_win + sh.n_dec + sh.n_stream;
   if (n_rows > 0) {
     pl.n_row_parts = pl.n_chunks;
     if (pl.n_chunks == 0) {
@@ -183,8 +183,8 @@ static int check_shape(const ShardDecodeShape* sh) {
   if (sh->rank < 32 || sh->rank > 192 || (sh->rank % 32)) return SHARD_E_ARG;
   if (sh->n_comp < 0 || sh->tok_begin < 0 || sh->tok_end < sh->tok_begin || sh->tok_end > sh->n_comp)
     return SHARD_E_ARG;
-  if (sh->n_sink < 0 || sh->n_win < 0 || sh->n_stream < 0) return SHARD_E_ARG;
-  if ((sh->tok_end - sh->tok_begin) + sh->n_sink + sh->n_win + sh->n_stream <= 0) return SHARD_E_ARG;
+  if (sh->n_sink < 0 || sh->n_win < 0 || sh->n_stream < 0 || sh->n_dec < 0) return SHARD_E_ARG;
+  if ((sh->tok_end - sh->tok_begin) + sh->n_sink + sh->n_win + sh->n_dec + sh->n_stream <= 0) return SHARD_E_ARG;
   return SHARD_OK;
 }
 
@@ -225,11 +225,13 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
       return SHARD_E_ARG;
     if (sh.n_sink > 0 && (!s.sink_k || !s.sink_v)) return SHARD_E_ARG;
     if (sh.n_win > 0 && (!s.win_k || !s.win_v)) return SHARD_E_ARG;
+    if (sh.n_dec > 0 && (!s.dec_k || !s.dec_v)) return SHARD_E_ARG;
     if (sh.n_stream > 0 && (!s.st_k_idx || !s.st_v_idx || !s.st_k_norm || !s.st_v_norm || !s.signs))
       return SHARD_E_ARG;
     if (((uintptr_t)s.k_coeffs & 15) || ((uintptr_t)s.k_wprep & 15) || ((uintptr_t)s.v_indices & 15) ||
         ((uintptr_t)s.v_centroids & 7) || ((uintptr_t)s.phase & 15) || ((uintptr_t)s.sink_k & 7) ||
         ((uintptr_t)s.sink_v & 7) || ((uintptr_t)s.win_k & 7) || ((uintptr_t)s.win_v & 7) ||
+        ((uintptr_t)s.dec_k & 7) || ((uintptr_t)s.dec_v & 7) ||
         ((uintptr_t)s.st_k_idx & 3) || ((uintptr_t)s.st_v_idx & 3) || ((uintptr_t)s.signs & 15) ||
         ((uintptr_t)s.v_ch & 7))
       return SHARD_E_ALIGN;
@@ -321,7 +323,7 @@ extern "C" int shard_b200_decode_attn_noalloc(const ShardSeq* seq_host, const Sh
                                 (size_t)SHARD_B200_STATIC_SCRATCH_BYTES, stream);
 }
 
-extern "C" int shard_b200_abi_version(void) { return 1; }
+extern "C" int shard_b200_abi_version(void) { return 2; }
 
 extern "C" const char* shard_b200_status_string(int status) {
   switch (status) {

@@ -111,14 +111,14 @@ __device__ __forceinline__ void append_new_token(const ShardSeq& sq, const Shard
   quantize_vec_warp(src, sq.signs, cbs, idx_out, norm_out, lane);
 }
 
-// Rows outside the compressed middle, in one index space: u < n_sink + n_win is an fp16 row
-// (sink rows first), the rest are streamed rows.  A warp takes rows u_first, u_first + u_step, ...;
+// Rows outside the compressed middle, in one index space: u < n_sink + n_win + n_dec is an fp16
+// row (sink rows first, then window, then the fp16 decode buffer), the rest are streamed rows.  A warp takes rows u_first, u_first + u_step, ...;
 // lane owns channels 4*lane..+3.  `qr` is the query as given (fp32 copy in shared memory), `cbs`
 // the stream codebook in shared memory (needed for streamed rows only).
 __device__ __forceinline__ void process_rows(SoftmaxState& st, const ShardSeq& sq, const ShardDecodeShape& sh,
                                              int kv, int u_first, int u_step,
                                              const float* __restrict__ qr, const float* __restrict__ cbs, int lane) {
-  const int n_fp = sh.n_sink + sh.n_win, n_rows = n_fp + sh.n_stream;
+  const int n_sw = sh.n_sink + sh.n_win, n_fp = n_sw + sh.n_dec, n_rows = n_fp + sh.n_stream;
   if (u_first >= n_rows) return;
   float4 sg = make_float4(0.f, 0.f, 0.f, 0.f);
   if (sh.n_stream > 0) sg = *reinterpret_cast<const float4*>(sq.signs + 4 * lane);
@@ -128,11 +128,11 @@ __device__ __forceinline__ void process_rows(SoftmaxState& st, const ShardSeq& s
   for (int u = u_first; u < n_rows; u += u_step) {
     float kx[4], vx[4];
     if (u < n_fp) {
-      const bool in_sink = u < sh.n_sink;
-      const int r = in_sink ? u : u - sh.n_sink;
-      const int rows = in_sink ? sh.n_sink : sh.n_win;
-      const __half* kb = reinterpret_cast<const __half*>(in_sink ? sq.sink_k : sq.win_k);
-      const __half* vb = reinterpret_cast<const __half*>(in_sink ? sq.sink_v : sq.win_v);
+      const bool in_sink = u < sh.n_sink, in_dec = u >= n_sw;
+      const int r = in_sink ? u : (in_dec ? u - n_sw : u - sh.n_sink);
+      const int rows = in_sink ? sh.n_sink : (in_dec ? sh.n_dec : sh.n_win);
+      const __half* kb = reinterpret_cast<const __half*>(in_sink ? sq.sink_k : (in_dec ? sq.dec_k : sq.win_k));
+      const __half* vb = reinterpret_cast<const __half*>(in_sink ? sq.sink_v : (in_dec ? sq.dec_v : sq.win_v));
       const size_t off = ((size_t)kv * rows + r) * HD + 4 * lane;
       const uint2 kr = *reinterpret_cast<const uint2*>(kb + off);
       const uint2 vr = *reinterpret_cast<const uint2*>(vb + off);

@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 52] = smid;
   }
 #endif
-  const int n_rows = sh.n_sink + sh.n_win + sh.n_stream;
+  const int n_rows = sh.n_sink + sh.n_win + sh.n_dec + sh.n_stream;
   // the CTA that owns the newest streamed row quantises it before anybody reads the stream
   const bool append_here = sh.append && p.n_row_parts > 0 && (n_rows - 1) % p.n_row_parts == part;
   float* rec_rows = p.ws + (((size_t)blockIdx.z * p.n_parts + p.n_chunks + part) * sh.n_q + (size_t)kv * GQA) * PART;

@@ -163,12 +163,13 @@ def decode_prepare(basis_f16, coeff_scale_f16, mean_f16, nkv, rank):
 
 
 def make_shape(n_q, nkv, rank, n_comp, tok_begin, tok_end, n_sink, n_win, n_stream, pos_q, partial_out=False,
-               append=False):
+               append=False, n_dec=0):
     sh = ShardDecodeShape()
     sh.n_q, sh.nkv, sh.rank, sh.n_comp = n_q, nkv, rank, n_comp
     sh.tok_begin, sh.tok_end = tok_begin, tok_end
     sh.n_sink, sh.n_win, sh.n_stream = n_sink, n_win, n_stream
     sh.pos_q, sh.partial_out, sh.append = int(pos_q), int(bool(partial_out)), int(bool(append))
+    sh.n_dec = int(n_dec)
     return sh
 
 

@@ -74,7 +74,34 @@ def build_cache(rc, k, v, inv_freq, streaming=False, k_target_cr=20.0):
     return cache
 
 
-def main(ref_root):
+def decode_buffer_fixture(rc, ra, inv_freq):
+    """configs[0] cache in the reference's DEFAULT mode (no stream: decoded tokens are appended to
+    the fp16 buffers decode_k / decode_v, cache.py:168-181): three decode steps, each one update
+    followed by fused_attention_compressed.  Only the tokens, queries and outputs are stored; the
+    compressed tensors are those of cfg0.npz (compression is seeded), which is asserted here."""
+    k, v, q = synth.make_kvq(2048, 0)
+    cache = build_cache(rc, k, v, inv_freq, streaming=False)
+    cache.compress()
+    layer = cache.layers[0]
+    gc = layer._gpu_compressed
+    ref = np.load(os.path.join(HERE, "cfg0.npz"))
+    for key in ("k_coeffs", "v_indices_u8", "k_basis_q", "v_centroids_f16"):
+        assert np.array_equal(t2n(gc[key]), ref[key]), key
+    cache._fused_decode_update = True
+    toks_k, toks_v, qs, outs = [], [], [], []
+    for j in range(3):
+        kt, vt, qt = synth.make_token(700 + j)
+        layer.update(kt, vt)
+        toks_k.append(kt)
+        toks_v.append(vt)
+        qs.append(qt)
+        outs.append(ra.fused_attention_compressed(qt, layer, 2048 + j, inv_freq, None))
+    assert gc["decode_k"].shape[2] == 3
+    save("cfg0_decbuf.npz", dec_k=t2n(torch.cat(toks_k, 2)), dec_v=t2n(torch.cat(toks_v, 2)),
+         dec_q=t2n(torch.cat(qs, 2)), dec_out=t2n(torch.cat(outs, 2)))
+
+
+def main(ref_root, only=None):
     rc = load_reference(ref_root)
     import shard.attention as ra
     import shard.rope as rr
@@ -83,6 +110,9 @@ def main(ref_root):
 
     torch.manual_seed(0)
     inv_freq = synth.rope_inv_freq()
+    if only == "decbuf":
+        decode_buffer_fixture(rc, ra, inv_freq)
+        return
 
     # ---- Lloyd-Max codebook, signs, inv_freq --------------------------------
     cb = rs.lloyd_max_codebook(128, 8)
@@ -244,9 +274,10 @@ def main(ref_root):
          st_k_norm=t2n(gc["k_norm_buf"][:s]), st_v_norm=t2n(gc["v_norm_buf"][:s]),
          mem_stream=np.array([cache.memory_bytes(), cache.clean_memory_bytes(),
                               cache.fp16_equivalent_bytes()], np.int64))
+    decode_buffer_fixture(rc, ra, inv_freq)
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        sys.exit("usage: make_golden.py <reference checkout>")
-    main(sys.argv[1])
+    if len(sys.argv) not in (2, 3):
+        sys.exit("usage: make_golden.py <reference checkout> [decbuf]")
+    main(sys.argv[1], sys.argv[2] if len(sys.argv) == 3 else None)

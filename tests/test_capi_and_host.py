@@ -35,8 +35,8 @@ def test_library_exports_every_declared_symbol():
 def test_struct_layouts_match_header():
     import ctypes as C
     from shard_b200 import _lib
-    assert C.sizeof(_lib.ShardSeq) == 19 * 8
-    assert C.sizeof(_lib.ShardDecodeShape) == 12 * 4
+    assert C.sizeof(_lib.ShardSeq) == 21 * 8
+    assert C.sizeof(_lib.ShardDecodeShape) == 13 * 4
 
 
 def test_argument_validation_without_gpu():

@@ -220,6 +220,34 @@ def test_decode_with_stream_against_reference(ops, codebook, golden_cfg0):
         assert tol_ok(out, exact, atol=EXACT_ATOL, rtol=EXACT_RTOL)
 
 
+def test_decode_with_fp16_decode_buffer_against_reference(ops, codebook, golden_cfg0):
+    """Non-streaming cache (the reference's default): decoded tokens live in gc["decode_k/v"] as
+    fp16 rows that grow by torch.cat; alone, and together with streamed rows."""
+    from gpu_helpers import layer_from_golden
+    g, d = golden_cfg0, load_golden("cfg0_decbuf.npz")
+    layer, gc_np = layer_from_golden(g)
+    gc = layer._gpu_compressed
+    for j in range(3):
+        dec = (d["dec_k"][0][:, :j + 1], d["dec_v"][0][:, :j + 1])
+        gc["decode_k"], gc["decode_v"] = T(dec[0]).unsqueeze(0), T(dec[1]).unsqueeze(0)
+        out = _decode(layer, d["dec_q"][0, :, j, :], 2048 + j)
+        assert tol_ok(out, d["dec_out"][0, :, j, :])                          # the reference's own output
+        exact, *_ = O.attention_exact(d["dec_q"][0, :, j, :], gc_np, 2048 + j, O.default_inv_freq(), decode=dec)
+        assert tol_ok(out, exact, atol=EXACT_ATOL, rtol=EXACT_RTOL)
+    # both kinds of appended rows at once
+    cb = O.lloyd_max_codebook(128, 8)
+    s = 5
+    gc["signs"] = T(g["st_signs"])
+    gc["k_idx_buf"], gc["v_idx_buf"] = T(g["st_k_idx"][:s]), T(g["st_v_idx"][:s])
+    gc["k_norm_buf"], gc["v_norm_buf"] = T(g["st_k_norm"][:s]), T(g["st_v_norm"][:s])
+    gc["stream_n"] = s
+    stream = dict(k_idx=g["st_k_idx"][:s, 0], v_idx=g["st_v_idx"][:s, 0], k_norm=g["st_k_norm"][:s, 0],
+                  v_norm=g["st_v_norm"][:s, 0], signs=g["st_signs"], codebook=cb)
+    out = _decode(layer, d["dec_q"][0, :, 2, :], 2060)
+    exact, *_ = O.attention_exact(d["dec_q"][0, :, 2, :], gc_np, 2060, O.default_inv_freq(), stream=stream, decode=dec)
+    assert tol_ok(out, exact, atol=EXACT_ATOL, rtol=EXACT_RTOL)
+
+
 def _check_random(n_comp, rank, n_sink, n_win, pos_q, compress_start=None, n_stream=0, seed=0, ops=None,
                   codebook=None, atol=None, rtol=None):
     atol = EXACT_ATOL if atol is None else atol

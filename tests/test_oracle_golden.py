@@ -150,6 +150,22 @@ def test_fused_attention_cfg0_with_stream(golden_cfg0):
     assert np.array_equal(kn, g["st_k_norm"][:, 0]) and np.array_equal(vn, g["st_v_norm"][:, 0])
 
 
+def test_fused_attention_cfg0_with_fp16_decode_buffer(golden_cfg0):
+    """The reference's default (non-streaming) mode: decoded tokens appended as fp16 rows."""
+    g, d = golden_cfg0, load_golden("cfg0_decbuf.npz")
+    gc = gc_from_golden(g)
+    inv_freq = O.default_inv_freq()
+    for j in range(3):
+        dec = (d["dec_k"][0][:, :j + 1], d["dec_v"][0][:, :j + 1])
+        out = O.fused_attention_compressed(d["dec_q"][0, :, j, :], gc, 2048 + j, inv_freq, decode=dec)
+        ref = d["dec_out"][0, :, j, :]
+        assert np.abs(out.astype(np.float32) - ref.astype(np.float32)).max() <= 1e-3
+        # the float64 evaluation of the same cache (the GPU tests' second yardstick) stays within
+        # the reference's own fp16 noise of it
+        exact, *_ = O.attention_exact(d["dec_q"][0, :, j, :], gc, 2048 + j, inv_freq, decode=dec)
+        assert np.abs(ref.astype(np.float64) - exact).max() <= 5e-3
+
+
 def test_fused_attention_chain512(golden_chain512):
     g = golden_chain512
     gc = gc_from_golden(g)
