@@ -198,7 +198,7 @@ def enable_llama_fused_attention(model=None):
         layer = cache.layers[self.layer_idx] if isinstance(cache, Cache) else None
         use_fused = (layer is not None and layer._gpu_compressed is not None
                      and hidden_states.shape[1] == 1 and hidden_states.shape[0] == 1
-                     and cache._rope_inv_freq is not None and cache._streaming)
+                     and cache._rope_inv_freq is not None)
         if not use_fused:
             return stock_forward(self, hidden_states, position_embeddings=position_embeddings,
                                  attention_mask=attention_mask, past_key_values=past_key_values, **kwargs)

@@ -529,3 +529,46 @@ def test_llama_generate_with_fused_attention():
         want = model(ref[:, :301]).logits[0, -1].float()
     assert torch.isfinite(nxt).all() and torch.isfinite(full).all()
     assert (nxt - want).abs().max().item() < 0.25 * want.abs().max().item() + 0.05
+
+
+def test_llama_generate_default_mode_uses_the_fused_kernel():
+    """The reference's default mode (no stream): new tokens go to the fp16 decode buffer and the
+    fused kernel attends to them; the generated ids equal those of the streaming mode's cache up to
+    quantisation of the few decoded tokens, and the decode buffer grows by one row per step."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from shard_b200 import Cache, enable_llama_fused_attention
+    import shard_b200.attention as A
+    torch.manual_seed(0)
+    cfg = LlamaConfig(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=1, head_dim=128, vocab_size=512, rope_theta=500000.0,
+                      max_position_embeddings=4096)
+    model = LlamaForCausalLM(cfg).half().to(DEV).eval()
+    assert enable_llama_fused_attention(model)
+    ids = torch.randint(0, 512, (1, 300), generator=torch.Generator().manual_seed(1)).to(DEV)
+    calls = {"n": 0}
+    real = A.decode_layer
+
+    def counting(*a, **k):
+        calls["n"] += 1
+        return real(*a, **k)
+
+    A.decode_layer = counting
+    try:
+        cache = Cache.from_model(model)                       # _streaming stays False
+        with torch.no_grad():
+            out = model.generate(ids, max_new_tokens=6, do_sample=False, past_key_values=cache, pad_token_id=0)
+    finally:
+        A.decode_layer = real
+    assert out.shape == (1, 306)
+    gc = cache.layers[1]._gpu_compressed
+    assert cache._compressed and "decode_k" in gc and gc["decode_k"].shape[2] >= 5 and "stream_n" not in gc
+    # every decode step of both layers went through the kernel, except layer 0's first one, whose
+    # update is what triggers the compression (as in the reference)
+    assert calls["n"] >= 2 * 5 - 1
+    with torch.no_grad():
+        cache2 = Cache.from_model(model)
+        model(ids, past_key_values=cache2, use_cache=True)
+        nxt = model(out[:, 300:301], past_key_values=cache2, use_cache=True).logits[0, -1].float()
+        want = model(out[:, :301]).logits[0, -1].float()
+    assert torch.isfinite(nxt).all()
+    assert (nxt - want).abs().max().item() < 0.25 * want.abs().max().item() + 0.05
