@@ -301,6 +301,15 @@ int shard_b200_v_hadamard_normalise(const void* v_f16, int64_t head_stride, int6
 int shard_b200_vq_assign(const float* x, const float* centroids, int64_t n, uint8_t* idx_u8,
                          int64_t* idx_i64, void* stream);
 
+/*
+ * One Lloyd iteration's heavy part: the assignment of shard_b200_vq_assign plus, in the same
+ * pass, the per-centroid sums (fp32 [256][4]) and counts (fp32 [256]) that the reference gets
+ * from two index_add_ calls in kmeans (src/shard/cache.py:29-32).  `sums` and `counts` must be
+ * zero on entry; the additions happen in no fixed order (as index_add_ on a GPU).
+ */
+int shard_b200_vq_assign_accumulate(const float* x, const float* centroids, int64_t n, uint8_t* idx_u8,
+                                    float* sums, float* counts, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

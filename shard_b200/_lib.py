@@ -46,6 +46,8 @@ _SIGNATURES = {
     "shard_b200_decode_attn_noalloc": (C.c_int, [C.c_void_p, C.POINTER(ShardDecodeShape), C.c_void_p, C.c_void_p,
                                                  C.c_void_p]),
     "shard_b200_lse_merge": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "shard_b200_vq_assign_accumulate": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                  C.c_void_p]),
     "shard_b200_peer_buffer_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
     "shard_b200_peer_alloc": (C.c_int, [C.c_size_t, C.c_void_p, C.c_void_p]),
     "shard_b200_peer_open": (C.c_int, [C.c_void_p, C.c_void_p]),

@@ -51,8 +51,8 @@ def hadamard(x):
 def kmeans(data, k, n_iter=30, seed=42, init=None):
     """Lloyd's algorithm as the reference runs it (src/shard/cache.py:21-39).
 
-    Assignment is the CUDA `vq_assign` kernel; the centroid update stays in
-    PyTorch.  Returns the updated centroids and the assignment made against the
+    Assignment and the per-centroid sums / counts come from one CUDA pass
+    (`vq_assign_accumulate`); the division and the stopping rule stay in PyTorch.  Returns the updated centroids and the assignment made against the
     previous ones.  `init` overrides the seeded random initial centroids.
     """
     n = data.shape[0]
@@ -63,13 +63,11 @@ def kmeans(data, k, n_iter=30, seed=42, init=None):
     else:
         centroids = init.to(dev, data.dtype).clone()
     idx_u8 = None
-    ones = torch.ones(n, device=dev, dtype=data.dtype)
+    sums = torch.zeros_like(centroids)
+    counts = torch.zeros(k, device=dev, dtype=data.dtype)
     for it in range(n_iter):
-        idx_u8, idx = ops.vq_assign(data, centroids)
-        sums = torch.zeros_like(centroids)
-        counts = torch.zeros(k, device=dev, dtype=data.dtype)
-        sums.index_add_(0, idx, data)
-        counts.index_add_(0, idx, ones)
+        # assignment and the sums / counts of the centroid update in one pass over the points
+        idx_u8 = ops.vq_assign_accumulate(data, centroids, sums, counts)
         filled = counts > 0
         new = centroids.clone()
         new[filled] = sums[filled] / counts[filled].unsqueeze(1)

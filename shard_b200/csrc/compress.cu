@@ -241,11 +241,20 @@ __global__ void __launch_bounds__(256) v_normalise_kernel(float* __restrict__ x,
 // ---------------------------------------------------------------------------
 // VQ assign: argmin_k ((x0-c0)^2 + (x1-c1)^2) + (x2-c2)^2) + (x3-c3)^2, first minimum
 // ---------------------------------------------------------------------------
+// With ACCUMULATE the kernel also does the k-means statistics of the same pass: per-centroid sums
+// and counts are collected in shared memory (atomics) and added to `sums` / `counts` once per CTA,
+// replacing two index_add_ passes over all points.  The order of those additions is not fixed,
+// exactly as with index_add_ on a GPU.
+template <bool ACCUMULATE>
 __global__ void __launch_bounds__(256) vq_assign_kernel(const float4* __restrict__ x,
                                                         const float4* __restrict__ centroids, int64_t n,
-                                                        uint8_t* __restrict__ idx_u8, int64_t* __restrict__ idx_i64) {
+                                                        uint8_t* __restrict__ idx_u8, int64_t* __restrict__ idx_i64,
+                                                        float* __restrict__ sums, float* __restrict__ counts) {
   __shared__ float4 cb[256];
+  __shared__ float acc_s[ACCUMULATE ? 256 * 5 : 1];
   cb[threadIdx.x] = centroids[threadIdx.x];
+  if (ACCUMULATE)
+    for (int i = threadIdx.x; i < 256 * 5; i += 256) acc_s[i] = 0.f;
   __syncthreads();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const float4 p = x[i];
@@ -263,6 +272,22 @@ __global__ void __launch_bounds__(256) vq_assign_kernel(const float4* __restrict
     }
     idx_u8[i] = (uint8_t)arg;
     if (idx_i64) idx_i64[i] = arg;
+    if (ACCUMULATE) {
+      atomicAdd(&acc_s[arg * 5 + 0], p.x);
+      atomicAdd(&acc_s[arg * 5 + 1], p.y);
+      atomicAdd(&acc_s[arg * 5 + 2], p.z);
+      atomicAdd(&acc_s[arg * 5 + 3], p.w);
+      atomicAdd(&acc_s[arg * 5 + 4], 1.f);
+    }
+  }
+  if (ACCUMULATE) {
+    __syncthreads();
+    const int k = threadIdx.x;
+    if (acc_s[k * 5 + 4] > 0.f) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) atomicAdd(&sums[k * 4 + c], acc_s[k * 5 + c]);
+      atomicAdd(&counts[k], acc_s[k * 5 + 4]);
+    }
   }
 }
 
@@ -355,8 +380,21 @@ extern "C" int shard_b200_vq_assign(const float* x, const float* centroids, int6
   if (n == 0) return SHARD_OK;
   const int64_t want = (n + 255) / 256;
   const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
-  vq_assign_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const float4*)x, (const float4*)centroids, n, idx_u8,
-                                                              idx_i64);
+  vq_assign_kernel<false><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float4*)x, (const float4*)centroids, n,
+                                                                     idx_u8, idx_i64, nullptr, nullptr);
+  SHARD_CHECK_LAUNCH();
+  return SHARD_OK;
+}
+
+extern "C" int shard_b200_vq_assign_accumulate(const float* x, const float* centroids, int64_t n, uint8_t* idx_u8,
+                                               float* sums, float* counts, void* stream) {
+  if (!x || !centroids || !idx_u8 || !sums || !counts || n < 0) return SHARD_E_ARG;
+  if (((uintptr_t)x | (uintptr_t)centroids) & 15) return SHARD_E_ALIGN;
+  if (n == 0) return SHARD_OK;
+  const int64_t want = (n + 255) / 256;
+  const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
+  vq_assign_kernel<true><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float4*)x, (const float4*)centroids, n,
+                                                                    idx_u8, nullptr, sums, counts);
   SHARD_CHECK_LAUNCH();
   return SHARD_OK;
 }

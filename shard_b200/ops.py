@@ -129,6 +129,23 @@ def vq_assign(x, centroids, want_i64=True):
     return u8, i64
 
 
+def vq_assign_accumulate(x, centroids, sums, counts):
+    """vq_assign + per-centroid sums (256, 4) and counts (256,) of the same pass (both zeroed here);
+    returns the u8 indices."""
+    require_cuda(x, centroids, sums, counts)
+    n = x.shape[0]
+    if x.shape[1] != 4 or tuple(centroids.shape) != (256, 4):
+        raise _lib.ShardError("vq_assign supports 4-dim sub-vectors and a 256-entry codebook")
+    u8 = torch.empty(n, dtype=torch.uint8, device=x.device)
+    sums.zero_()
+    counts.zero_()
+    check(_lib.load().shard_b200_vq_assign_accumulate(ptr(_c(x, torch.float32)), ptr(_c(centroids, torch.float32)), n,
+                                                      ptr(u8), ptr(_c(sums, torch.float32)),
+                                                      ptr(_c(counts, torch.float32)), cur_stream()),
+          "vq_assign_accumulate")
+    return u8
+
+
 # --------------------------------------------------------------------------- decode
 def phase_table_numel(n):
     """fp16 elements of the phase table of `n` tokens (tokens are padded to blocks of 32)."""

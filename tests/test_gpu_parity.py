@@ -159,6 +159,26 @@ def test_vq_assign_ties_pick_first(ops):
     assert np.array_equal(N(u8), (2 * np.arange(128)).astype(np.uint8))
 
 
+def test_vq_assign_accumulate_matches_assign_plus_index_add(ops):
+    """The fused Lloyd pass: same codes as vq_assign, counts exact, sums equal to a float64
+    accumulation of the assigned points up to fp32 summation error."""
+    g = load_golden("vq.npz")
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((300001, 4)).astype(np.float32) * 0.4
+    cent = g["km_init"].astype(np.float32)
+    u8_ref, _ = ops.vq_assign(T(x), T(cent))
+    sums = torch.full((256, 4), 7.0, device=DEV)
+    counts = torch.full((256,), 7.0, device=DEV)
+    u8 = ops.vq_assign_accumulate(T(x), T(cent), sums, counts)
+    assert torch.equal(u8, u8_ref)
+    idx = N(u8).astype(np.int64)
+    want_counts = np.bincount(idx, minlength=256).astype(np.float64)
+    want_sums = np.zeros((256, 4))
+    np.add.at(want_sums, idx, x.astype(np.float64))
+    assert np.array_equal(N(counts).astype(np.float64), want_counts)
+    assert np.allclose(N(sums), want_sums, rtol=1e-4, atol=1e-2)
+
+
 def test_kmeans_against_reference(ops):
     from shard_b200.cache import kmeans
     g = load_golden("vq.npz")
