@@ -57,6 +57,12 @@ def test_argument_validation_without_gpu():
     assert lib.shard_b200_decode_attn(C.addressof(seq), 1, C.byref(sh), None, None, None, 0, None) == -1
     assert lib.shard_b200_k_quantize_pack(None, None, 10, 4, None, None, None, 0, None) == -1
     assert lib.shard_b200_lse_merge(None, 2, 32, None, None) == -1
+    # sequence-split exchange: buffer = flags (2 slots x world x nkv u32, rounded to 256 B) + 2 slots of records
+    assert lib.shard_b200_peer_buffer_bytes(2, 8) == 256 + 2 * 2 * 32 * 132 * 4
+    assert lib.shard_b200_peer_buffer_bytes(17, 8) == 0
+    assert lib.shard_b200_seqsplit_merge(None, None, 0, 2, 8, 1, None, None, None) == -1
+    assert lib.shard_b200_vq_assign_accumulate(None, None, 10, None, None, None, None) == -1
+    assert lib.shard_b200_phase_table_bytes(33) == 64 * 256
 
 
 def test_ops_refuse_cpu_tensors():
