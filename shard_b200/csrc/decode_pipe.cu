@@ -83,13 +83,13 @@ __device__ __forceinline__ void umma_commit_1t(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// Barrier among a subset of the CTA's warps (id 1..15, `count` threads) that also ORs a flag
-// over the participants.  The roles use it to agree on giving up: a warp whose bounded wait
-// failed never leaves its siblings alone at a barrier -- everybody reaches the barrier, learns
-// the combined flag and leaves the tile loop together.
+// Plain barrier among a subset of the CTA's warps (id 1..15, `count` threads).
 __device__ __forceinline__ void named_bar_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
+// The same barrier, also ORing a flag over the participants.  The roles use it to agree on giving
+// up: a warp whose bounded wait failed never leaves its siblings alone at a barrier -- everybody
+// reaches the barrier, learns the combined flag and leaves the tile loop together.
 __device__ __forceinline__ bool named_bar_or(int id, int count, bool flag) {
   uint32_t out;
   asm volatile(
@@ -100,8 +100,8 @@ __device__ __forceinline__ bool named_bar_or(int id, int count, bool flag) {
 }
 
 #ifdef SHARD_TC_DEBUG
-// development aid: per-CTA, per-role phase accounting (role 0: consumer warp 0, 1: unpack warp 12,
-// 2: MMA thread); slot k accumulates the cycles that ended at stamp k
+// development aid: per-CTA, per-role phase accounting (role 0: consumer warp 0, 1: unpack warp 12);
+// slot k accumulates the cycles that ended at stamp k
 __device__ long long* g_pp_debug = nullptr;
 #define PP_T0(role) long long pp_last__ = clock64(); \
   long long* pp_rec__ = g_pp_debug ? reinterpret_cast<long long*>(smem + pp_smem_bytes(NW) - 1024 - 512) + 16 * (role) : nullptr
