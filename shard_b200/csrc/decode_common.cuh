@@ -205,7 +205,8 @@ __device__ __forceinline__ void partial_merge(const float* scratch, float* __res
   }
 }
 
-// Fused combine.  Every CTA of one (sequence, KV head) calls this after its record is written.
+// Fused combine.  Every CTA of one (sequence, KV head) calls this after its record is written
+// (`released`: the caller has already issued __threadfence + __syncthreads after those writes).
 // Each takes a ticket; the CTA that draws the last one sees all records of that KV head
 // (release/acquire through the fences around the ticket), merges them for the head's four
 // query heads exactly as decode_combine_kernel does (same order, same operations), and puts
@@ -213,12 +214,14 @@ __device__ __forceinline__ void partial_merge(const float* scratch, float* __res
 // are free; NTHREADS >= GQA*HD.  Thread tid handles head tid/128, channel tid%128.
 template <int NTHREADS>
 __device__ __forceinline__ void ticket_combine(const DecodeParams& p, const ShardSeq& sq, int kv, int b,
-                                               float* sm_raw, int tid) {
+                                               float* sm_raw, int tid, bool released = false) {
   volatile float* sm = sm_raw;   // exchanged between threads: every access must reach shared memory
   static_assert(NTHREADS >= GQA * HD, "one thread per (head, channel)");
   __shared__ int last_s;
-  __threadfence();
-  __syncthreads();
+  if (!released) {               // the caller has not yet fenced its record writes and synchronised the CTA
+    __threadfence();
+    __syncthreads();
+  }
   if (tid == 0) {
     int* ctr = p.tickets + b * p.sh.nkv + kv;
     const int last = atomicAdd(ctr, 1) == p.n_ctas - 1;

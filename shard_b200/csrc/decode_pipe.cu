@@ -593,22 +593,23 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   }
 
   // ---- epilogue: merge the 12 token-warps' states per head and emit the record -------------------
-  __syncthreads();
-  float* acc_s = reinterpret_cast<float*>(v_s);                   // [3 groups][16][128]
+  // every consumer group parks its state in its own V tile (its last MMA3 has completed), so one
+  // CTA barrier separates the tile loops from the merge
+  const float ch_scale = __half2float(reinterpret_cast<const __half*>(sq.v_ch)[kv * HD + (tid & 127)]);
   if (warp < PP_CONS_WARPS) {
     const int g = warp >> 2, quad = warp & 3, m = quad * 32 + lane;
+    float* acc_g = reinterpret_cast<float*>(v_s + g * PP_V_BYTES);   // [16][128]
 #pragma unroll
     for (int h = 0; h < GQA; ++h) {
       const float l = warp_sum(run_l[h]);
       if (lane == 0) { m_s[16 * g + 4 * quad + h] = run_m[h]; l_s[16 * g + 4 * quad + h] = l; }
     }
 #pragma unroll
-    for (int j = 0; j < 16; ++j) acc_s[(16 * g + j) * HD + m] = acc[j];
+    for (int j = 0; j < 16; ++j) acc_g[j * HD + m] = acc[j];
   }
   __syncthreads();
   {
     const int h = tid >> 7, m = tid & 127;              // 512 threads: one (head, channel) each
-    const float ch = __half2float(reinterpret_cast<const __half*>(sq.v_ch)[kv * HD + m]);
     float M = neg_inf();
 #pragma unroll
     for (int e = 0; e < 12; ++e) M = fmaxf(M, m_s[16 * (e >> 2) + 4 * (e & 3) + h]);
@@ -619,11 +620,11 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       const float mv = m_s[idx];
       const float wt = (mv == neg_inf()) ? 0.f : exp2f((mv - M) * LOG2E);
       L = fmaf(wt, l_s[idx], L);
-      a = fmaf(wt, acc_s[idx * HD + m], a);
+      a = fmaf(wt, reinterpret_cast<const float*>(v_s + (e >> 2) * PP_V_BYTES)[(4 * (e & 3) + h) * HD + m], a);
     }
     float* rec = rec_base + h * PART;
     if (m == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
-    rec[4 + m] = a * ch;
+    rec[4 + m] = a * ch_scale;
   }
   if (tid == 0 && *abort_s) {
     // gave up somewhere: do not leave while a bulk copy may still be landing in this CTA's memory
@@ -632,13 +633,15 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       if (c_cnt[b] > 0) mbar_wait(C_FULL(b), (uint32_t)((c_cnt[b] - 1) & 1), abort_s);
     if (p.status) atomicExch(p.status, 1);
   }
+  // one barrier serves the hand-back of tensor memory and the release of this CTA's records
+  __threadfence();
   tc_fence_before();
   __syncthreads();
   if (warp == PP_UNPACK_WARP0) tmem_dealloc(tmem_base, PP_TMEM_COLS);
 #ifdef SHARD_TC_DEBUG
   if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 43] = clock64() - pp_kstart__;
 #endif
-  ticket_combine<PP_THREADS>(p, sq, kv, blockIdx.z, reinterpret_cast<float*>(w_s), tid);
+  ticket_combine<PP_THREADS>(p, sq, kv, blockIdx.z, reinterpret_cast<float*>(w_s), tid, true);
 #ifdef SHARD_TC_DEBUG
   if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 49] += clock64() - pp_kstart__;
   if (g_pp_debug && tid == 0) {
