@@ -113,8 +113,12 @@ def ptr(t):
 
 
 def cur_stream():
+    """Raw handle of the current CUDA stream of the current device."""
     import torch
-    return torch.cuda.current_stream().cuda_stream
+    try:
+        return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
+    except AttributeError:
+        return torch.cuda.current_stream().cuda_stream
 
 
 def require_cuda(*tensors):
