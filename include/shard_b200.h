@@ -89,6 +89,7 @@ typedef struct ShardDecodeShape {
   int32_t partial_out;    /* 0: out = fp16 attention; 1: out = fp32 (m, l, acc) partial  */
   int32_t append;         /* 1: first quantise new_k/new_v into stream row n_stream-1 (fused append) */
   int32_t n_dec;          /* rows of the fp16 decode buffer (dec_k / dec_v)              */
+  int32_t no_overlap;     /* 1: plain launch, no early start behind the preceding kernel (see decode_attn) */
 } ShardDecodeShape;
 
 /*
@@ -150,15 +151,32 @@ size_t shard_b200_decode_workspace_bytes(const ShardDecodeShape* shape_host, int
  * The head of the workspace (a status word, then one arrival counter per sequence and KV head:
  * 16 + 4*batch*nkv bytes rounded up to 16) must be zero before the first call that uses the
  * workspace; every call leaves it zero again unless a bounded wait inside the kernel gave up,
- * in which case the status word is left at 1 and the output of that call is undefined.
- * The kernel is launched with programmatic stream serialization: when the work in front of it
- * in the stream is another decode call it may start fetching k_coeffs, k_wprep, v_indices and
- * v_centroids before that call has finished (no decode call writes them); everything else is
- * read and written only after the preceding work has completed.
+ * in which case the status word is left at 1 and the output of that call is undefined
+ * (read it with shard_b200_decode_status).
+ * The kernel is launched with programmatic stream serialization: its CTAs may start while the
+ * kernel directly in front of it in the stream is still running, and before waiting for that
+ * kernel they read k_wprep, k_coeffs, v_indices, v_centroids, the stream codebook and (batch > 1)
+ * the ShardSeq table.  So the kernel directly in front must not be one that WRITES any of those
+ * (shard_b200_decode_prepare, the kernels that produce the codes, a copy into the table): for
+ * the first decode call behind such work set shape.no_overlap = 1, which launches the plain way
+ * (or set SHARD_B200_PDL=0 in the environment to do so always).  Everything else -- query, new
+ * token, stream rows, phase table, workspace, output -- is read and written only after the
+ * preceding work has completed.
  */
 int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const ShardDecodeShape* shape_host,
                            const float* inv_freq, const float* codebook, void* workspace,
                            size_t workspace_bytes, void* stream);
+
+/*
+ * Reads the status word a decode launch leaves at the head of its workspace: waits for
+ * `stream`, stores the word in *status_host_out (0 = every launch since the last query
+ * completed normally, 1 = a bounded wait inside a kernel gave up and that call's output is
+ * undefined) and, if it was set, clears it.  workspace == NULL names the built-in scratch of
+ * shard_b200_decode_attn_noalloc on the current device.  Meant to be called once per step or
+ * per request, not per launch.  No reference counterpart (the reference has no device-side
+ * waits).
+ */
+int shard_b200_decode_status(void* workspace, int32_t* status_host_out, void* stream);
 
 /*
  * Size of the scratch area that lives inside the library's device image and is used by
@@ -186,7 +204,8 @@ int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const ShardDecod
  *     (cudaGetSymbolAddress, with that device current) and remembers it; make that
  *     first call before starting any stream capture.
  *   - All calls on a device share the one area, and it keeps the previous call's
- *     contents (the part that must start at zero is cleared on `stream` by each call).
+ *     contents (the part that must start at zero is cleared on `stream` by each call;
+ *     the status word is kept until shard_b200_decode_status(NULL, ...) has reported it).
  *     Two calls whose kernels can overlap on the GPU -- different streams without an
  *     ordering between them -- race on it and give wrong results; serialise them.
  */
@@ -212,11 +231,19 @@ int shard_b200_lse_merge(const float* parts, int32_t n_parts, int32_t n_q, void*
  * hot path), hands the 64-byte handle to the other ranks by any means, and opens theirs with
  * shard_b200_peer_open.  shard_b200_seqsplit_merge then takes this rank's fp32 [4*nkv][132]
  * partial (the output of shard_b200_decode_attn with shape.partial_out), stores it into every
- * rank's buffer with plain peer stores, publishes `epoch`, waits -- bounded, about 0.2 s, after
- * which *status_dev is set to 1 and out is left unwritten -- for all ranks' records of the same
- * epoch and merges them in rank order into out_f16 (fp16 [4*nkv][128]), bit-identical on every
- * rank.  `bufs_host` is a HOST array of `world` device pointers (entry `rank` = own buffer);
- * `epoch` starts at 1 and grows by 1 per call, in step on all ranks.
+ * rank's buffer with plain peer stores, publishes `epoch`, waits -- bounded by `timeout_us`
+ * microseconds of the GPU's global timer (0 = 200 000), after which *status_dev is set to 1 and
+ * out is left unwritten -- for all ranks' records of the same epoch and merges them in rank order
+ * into out_f16 (fp16 [4*nkv][128]), bit-identical on every rank.  `bufs_host` is a HOST array of
+ * `world` device pointers (entry `rank` = own buffer); `epoch` starts at 1 and grows by 1 per
+ * call, in step on all ranks.
+ *
+ * Faster form of the same step: shard_b200_decode_attn_seqsplit is shard_b200_decode_attn for one
+ * sequence (shape.partial_out must be 1) whose combining CTAs deliver the record straight into
+ * every rank's buffer and publish `epoch` -- the decode launch does the exchange -- and
+ * shard_b200_seqsplit_wait_merge is the wait + merge half alone, launched so that it is already
+ * polling while the decode launch in front of it runs.  seq_host->out may be NULL there.  Per
+ * epoch a rank uses either shard_b200_seqsplit_merge or this pair; ranks may differ.
  */
 size_t shard_b200_peer_buffer_bytes(int32_t world, int32_t nkv);
 int shard_b200_peer_alloc(size_t bytes, void** ptr_out, void* handle_out_64);
@@ -224,7 +251,15 @@ int shard_b200_peer_open(const void* handle_64, void** ptr_out);
 int shard_b200_peer_close(void* ptr);
 int shard_b200_peer_free(void* ptr);
 int shard_b200_seqsplit_merge(const float* my_part, void* const* bufs_host, int32_t rank, int32_t world,
-                              int32_t nkv, uint32_t epoch, void* out_f16, int* status_dev, void* stream);
+                              int32_t nkv, uint32_t epoch, void* out_f16, int* status_dev,
+                              uint32_t timeout_us, void* stream);
+int shard_b200_decode_attn_seqsplit(const ShardSeq* seq_host, const ShardDecodeShape* shape_host,
+                                    const float* inv_freq, const float* codebook, void* workspace,
+                                    size_t workspace_bytes, void* const* bufs_host, int32_t rank,
+                                    int32_t world, uint32_t epoch, void* stream);
+int shard_b200_seqsplit_wait_merge(void* const* bufs_host, int32_t rank, int32_t world, int32_t nkv,
+                                   uint32_t epoch, void* out_f16, int* status_dev, uint32_t timeout_us,
+                                   void* stream);
 
 /*
  * 8-bit Lloyd-Max quantisation of one new K and V token per KV head and append

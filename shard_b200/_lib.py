@@ -29,7 +29,7 @@ class ShardDecodeShape(C.Structure):
     """Mirror of `struct ShardDecodeShape`."""
     _fields_ = [(name, C.c_int32) for name in (
         "n_q", "nkv", "rank", "n_comp", "tok_begin", "tok_end",
-        "n_sink", "n_win", "n_stream", "pos_q", "partial_out", "append", "n_dec")]
+        "n_sink", "n_win", "n_stream", "pos_q", "partial_out", "append", "n_dec", "no_overlap")]
 
 
 _SIGNATURES = {
@@ -54,7 +54,13 @@ _SIGNATURES = {
     "shard_b200_peer_close": (C.c_int, [C.c_void_p]),
     "shard_b200_peer_free": (C.c_int, [C.c_void_p]),
     "shard_b200_seqsplit_merge": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_uint32,
-                                            C.c_void_p, C.c_void_p, C.c_void_p]),
+                                            C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
+    "shard_b200_decode_attn_seqsplit": (C.c_int, [C.c_void_p, C.POINTER(ShardDecodeShape), C.c_void_p, C.c_void_p,
+                                                  C.c_void_p, C.c_size_t, C.c_void_p, C.c_int32, C.c_int32,
+                                                  C.c_uint32, C.c_void_p]),
+    "shard_b200_seqsplit_wait_merge": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_uint32,
+                                                 C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
+    "shard_b200_decode_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p]),
     "shard_b200_stream_quantize": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                              C.c_void_p]),
     "shard_b200_stream_dequant": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
@@ -121,7 +127,20 @@ def cur_stream():
         return torch.cuda.current_stream().cuda_stream
 
 
-def require_cuda(*tensors):
+def require_cuda(*tensors, current=None):
+    """Every tensor must live on the CUDA device that is current: the kernels are launched on
+    the current device's current stream with raw pointers, so a tensor of another GPU would be
+    read through a wrong (or peer) address.  `current` overrides the device index asked from
+    torch (used by tests without a GPU)."""
+    cur = current
     for t in tensors:
-        if t is not None and not t.is_cuda:
+        if t is None:
+            continue
+        if not t.is_cuda:
             raise ShardError("shard_b200 kernels need CUDA tensors; there is no CPU fallback")
+        if cur is None:
+            import torch
+            cur = torch.cuda.current_device()
+        if t.device.index is not None and t.device.index != cur:
+            raise ShardError(f"tensor lives on cuda:{t.device.index} but the current device is cuda:{cur}; "
+                             "make the tensor's device current (torch.cuda.device) before the call")

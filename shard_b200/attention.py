@@ -87,17 +87,22 @@ def _launch_state(gc, cache, dev, nkv, n_q, t0, t1, with_fp16_segments, partial_
     return ls
 
 
-def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_fp16_segments=True, out=None):
+def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_fp16_segments=True, out=None,
+                 push=None):
     """Run the fused decode for one layer.
 
     q_rope: (1, n_q, 1, 128) fp16 CUDA.  `tok_range` limits the middle segment to
     [begin, end) (sequence-split mode); `partial_out` returns the fp32
     (n_q, 132) record (max, sum-exp, 0, 0, acc[128]) instead of fp16 attention.
+    `push` (a `parallel.PeerExchange`, with `partial_out`) makes the launch deliver that
+    record into every rank's exchange buffer itself.
+
+    A bounded wait that gives up inside the kernel leaves a status word in the cache's
+    workspace; `Cache.check()` reads it (once per step or request, it synchronises).
     """
     gc = layer._gpu_compressed
     cache = layer._cache_ref
-    if not q_rope.is_cuda:
-        raise _lib.ShardError("shard_b200 kernels need CUDA tensors; there is no CPU fallback")
+    _lib.require_cuda(q_rope, gc["k_wprep"])
     B, n_q, s_q, hd = q_rope.shape
     nkv = cache._n_kv_heads
     if B != 1 or s_q != 1:
@@ -140,15 +145,21 @@ def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_f
     q2 = q_rope.reshape(n_q, hd)
     if not q2.is_contiguous():
         q2 = q2.contiguous()
-    if out is None:
+    if push is not None and not partial_out:
+        raise _lib.ShardError("a launch that delivers to the peers emits the partial record")
+    if out is None and push is None:
         out = (torch.empty(n_q, _lib.PART_STRIDE, dtype=torch.float32, device=dev) if partial_out
                else torch.empty(n_q, hd, dtype=torch.float16, device=dev))
-    elif not out.is_contiguous() or out.numel() != n_q * (_lib.PART_STRIDE if partial_out else hd):
+    elif out is not None and (not out.is_contiguous() or out.numel() != n_q * (_lib.PART_STRIDE if partial_out else hd)):
         raise _lib.ShardError("out must be a contiguous (n_q, 128) fp16 or (n_q, 132) fp32 tensor")
-    seq.q, seq.out = q2.data_ptr(), out.data_ptr()
+    # with `push` and no `out` the record only goes to the exchange buffers
+    seq.q, seq.out = q2.data_ptr(), (None if out is None else out.data_ptr())
     seq.phase = _phase_for(cache, gc, pos_q, t0, t1, dev).data_ptr() if t1 > t0 else None
     shape.n_stream, shape.pos_q, shape.append = n_stream, int(pos_q), int(pending is not None)
     shape.n_dec = n_dec
+    # the first launch on a freshly built dictionary follows the kernels that wrote its codes and
+    # weights: it must not start early behind them
+    shape.no_overlap = int(gc.pop("_fresh", False))
     need = ls.need
     if t1 == t0:                                       # rows only: scratch grows with the rows
         need = ops.decode_workspace_bytes(shape, 1)
@@ -156,7 +167,10 @@ def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_f
     if ws is None or ws.numel() < need or ws.device != dev:
         # zero-filled: the header's status word and arrival counters must start at zero
         ws = cache._decode_ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dev)
-    ops.decode_attn(seq, 1, shape, ls.inv_ptr, ls.cb_ptr if n_stream > 0 else None, ws)
+    if push is not None:
+        push.launch_decode(seq, shape, ls.inv_ptr, ls.cb_ptr if n_stream > 0 else None, ws)
+    else:
+        ops.decode_attn(seq, 1, shape, ls.inv_ptr, ls.cb_ptr if n_stream > 0 else None, ws)
     return out
 
 

@@ -487,6 +487,13 @@ class Cache(HFCache):
         layer._values = None
         layer._needs_decompress = True
 
+    def check(self):
+        """Raise `ShardError` if a decode launch on this cache gave up on one of its bounded
+        in-kernel waits since the last check (its output is then undefined).  Waits for the
+        current stream; call it once per step or per request, not per layer."""
+        if self._decode_ws is not None:
+            ops.decode_status_check(self._decode_ws)
+
     def _inv_freq(self, dev):
         if self._inv_freq_dev is None or self._inv_freq_dev.device != torch.device(dev):
             self._inv_freq_dev = self._rope_inv_freq.to(dev, torch.float32).contiguous()
@@ -586,4 +593,5 @@ def attach_kernel_format(gc, nkv):
     gc["k_rank_kernel"] = rank_k
     gc["k_coeffs_kernel"] = coeffs
     gc["k_wprep"] = ops.decode_prepare(basis, cscale, gc["k_mean_f16"], nkv, rank_k)
+    gc["_fresh"] = True      # the next decode launch follows the kernels that wrote these tensors
     return gc

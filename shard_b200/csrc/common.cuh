@@ -15,6 +15,27 @@
 
 namespace shard {
 
+constexpr int MAX_DEVICES = 64;   // per-device host-side state (SM counts, kernel attributes, ...)
+
+// Number of SMs of the current device, asked from the runtime once per device.  Grids of the
+// persistent / one-wave kernels are sized from it.  Returns 0 if the query fails.
+inline int sm_count() {
+  static int cached[MAX_DEVICES] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return 0;
+  int n = cached[dev];               // a racing first call writes the same value twice
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached[dev] = n;
+  }
+  return n;
+}
+// grid size for a grid-stride kernel: enough blocks for `want`, at most `per_sm` per SM
+inline int capped_blocks(long long want, int per_sm) {
+  const long long cap = (long long)(sm_count() > 0 ? sm_count() : 1) * per_sm;
+  return (int)(want < cap ? (want > 0 ? want : 1) : cap);
+}
+
 constexpr int HD = 128;           // head_dim
 constexpr int HD2 = 64;           // rotary pairs per head
 constexpr int GQA = 4;            // query heads per KV head

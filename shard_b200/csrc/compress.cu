@@ -337,7 +337,7 @@ extern "C" int shard_b200_k_quantize_pack(const float* proj, const int32_t* allo
   kq_absmax_kernel<<<row_blocks, 256, 0, st>>>(proj, alloc_bits, n, keep, ws);
   kq_scale_kernel<<<(keep + 255) / 256, 256, 0, st>>>(ws, keep, coeff_scale_out);
   const size_t total = (size_t)n * (keep / 2);
-  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  const int blocks = capped_blocks((long long)((total + 255) / 256), 16);
   kq_pack_kernel<<<blocks, 256, 0, st>>>(proj, alloc_bits, n, keep, ws, coeff_scale_out, packed_out);
   SHARD_CHECK_LAUNCH();
   return SHARD_OK;
@@ -347,7 +347,7 @@ extern "C" int shard_b200_int4_pack(const int8_t* q, int64_t n_values, uint8_t* 
   if (!q || !packed_out || n_values < 0) return SHARD_E_ARG;
   if (n_values == 0) return SHARD_OK;
   const int64_t n_bytes = (n_values + 1) / 2;
-  const int blocks = (int)((n_bytes + 255) / 256 < 148 * 16 ? (n_bytes + 255) / 256 : 148 * 16);
+  const int blocks = capped_blocks((n_bytes + 255) / 256, 16);
   int4_pack_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(q, n_values, packed_out);
   SHARD_CHECK_LAUNCH();
   return SHARD_OK;
@@ -362,12 +362,12 @@ extern "C" int shard_b200_v_hadamard_normalise(const void* v_f16, int64_t head_s
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e = cudaMemsetAsync(ch_max_out, 0, (size_t)nkv * HD * sizeof(float), st);
   if (e != cudaSuccess) return (int)e;
-  const int bx = (n + 7) / 8 < 148 * 2 ? (n + 7) / 8 : 148 * 2;
+  const int bx = capped_blocks((n + 7) / 8, 2);
   v_rotate_kernel<<<dim3(bx, nkv), 256, 0, st>>>((const __half*)v_f16, head_stride, tok_stride, nkv, n, x_out,
                                                  (uint32_t*)ch_max_out);
   v_clamp_kernel<<<(nkv * HD + 255) / 256, 256, 0, st>>>(ch_max_out, nkv * HD);
   const size_t total4 = (size_t)nkv * n * 32;
-  const int blocks = (int)((total4 + 255) / 256 < 148 * 16 ? (total4 + 255) / 256 : 148 * 16);
+  const int blocks = capped_blocks((long long)((total4 + 255) / 256), 16);
   v_normalise_kernel<<<blocks, 256, 0, st>>>(x_out, ch_max_out, nkv, n);
   SHARD_CHECK_LAUNCH();
   return SHARD_OK;
@@ -379,7 +379,7 @@ extern "C" int shard_b200_vq_assign(const float* x, const float* centroids, int6
   if (((uintptr_t)x | (uintptr_t)centroids) & 15) return SHARD_E_ALIGN;
   if (n == 0) return SHARD_OK;
   const int64_t want = (n + 255) / 256;
-  const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
+  const int blocks = capped_blocks(want, 8);
   vq_assign_kernel<false><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float4*)x, (const float4*)centroids, n,
                                                                      idx_u8, idx_i64, nullptr, nullptr);
   SHARD_CHECK_LAUNCH();
@@ -392,7 +392,7 @@ extern "C" int shard_b200_vq_assign_accumulate(const float* x, const float* cent
   if (((uintptr_t)x | (uintptr_t)centroids) & 15) return SHARD_E_ALIGN;
   if (n == 0) return SHARD_OK;
   const int64_t want = (n + 255) / 256;
-  const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
+  const int blocks = capped_blocks(want, 8);
   vq_assign_kernel<true><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float4*)x, (const float4*)centroids, n,
                                                                     idx_u8, nullptr, sums, counts);
   SHARD_CHECK_LAUNCH();

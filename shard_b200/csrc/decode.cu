@@ -20,7 +20,7 @@
 namespace shard {
 
 constexpr int TILE_TOK = 128;          // tokens per tile of the middle segment
-constexpr int CTA_SLOTS = 148;         // the decode kernel keeps one CTA per SM of a B200
+constexpr int DEFAULT_CTA_SLOTS = 148;  // SMs of a B200; used only when no device can be asked
 constexpr int WS_STATUS_BYTES = 16;    // status word + padding at the very front of the scratch
 // header = status word, then one arrival counter per (sequence, KV head), rounded to 16 bytes
 static inline size_t ws_header_bytes(int batch, int nkv) {
@@ -37,8 +37,15 @@ struct DecodePlan {
   int n_chunks, tiles_per_chunk, tiles_rem, n_row_parts, n_parts, grid_x;
 };
 
+// the decode kernel keeps one CTA per SM: one CTA slot per SM of the current device
+static int cta_slots() {
+  const int n = sm_count();
+  return n > 0 ? n : DEFAULT_CTA_SLOTS;
+}
+
 static DecodePlan make_plan(const ShardDecodeShape& sh, int batch) {
   DecodePlan pl{};
+  const int CTA_SLOTS = cta_slots();
   const int n_tok = sh.tok_end - sh.tok_begin;
   const int n_tiles = (n_tok + TILE_TOK - 1) / TILE_TOK;
   const int groups = sh.nkv * batch;
@@ -155,7 +162,7 @@ extern "C" int shard_b200_phase_table(int32_t compress_start, int32_t pos_q, int
   if ((uintptr_t)out & 15) return SHARD_E_ALIGN;
   if (n_tok == 0) return SHARD_OK;
   const int total = ((n_tok + 31) / 32) * 256;
-  const int blocks = (total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8;
+  const int blocks = capped_blocks((total + 255) / 256, 8);
   phase_table_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(compress_start - pos_q, n_tok, inv_freq, (uint4*)out);
   SHARD_CHECK_LAUNCH();
   return SHARD_OK;
@@ -200,9 +207,9 @@ extern "C" size_t shard_b200_decode_workspace_bytes(const ShardDecodeShape* shap
   return ws_bytes(*shape_host, batch);
 }
 
-extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const ShardDecodeShape* shape_host,
-                                      const float* inv_freq, const float* codebook, void* workspace,
-                                      size_t workspace_bytes, void* stream) {
+static int decode_attn_impl(const ShardSeq* seqs, int32_t batch, const ShardDecodeShape* shape_host,
+                            const float* inv_freq, const float* codebook, void* workspace, size_t workspace_bytes,
+                            const PeerPush* push, void* stream) {
   if (!seqs || batch < 1 || !inv_freq || !workspace) return SHARD_E_ARG;
   int rc = check_shape(shape_host);
   if (rc != SHARD_OK) return rc;
@@ -219,7 +226,7 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
     p.one = *seqs;
     p.table = nullptr;
     const ShardSeq& s = p.one;
-    if (!s.q || !s.out) return SHARD_E_ARG;
+    if (!s.q || (!s.out && !push)) return SHARD_E_ARG;
     if (sh.tok_end > sh.tok_begin &&
         (!s.k_coeffs || !s.k_wprep || !s.v_indices || !s.v_centroids || !s.v_ch || !s.phase))
       return SHARD_E_ARG;
@@ -236,6 +243,7 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
         ((uintptr_t)s.v_ch & 7))
       return SHARD_E_ALIGN;
   } else {
+    if (push) return SHARD_E_ARG;
     p.table = seqs;
   }
   const size_t header = ws_header_bytes(batch, sh.nkv);
@@ -251,6 +259,7 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
   p.n_row_parts = pl.n_row_parts;
   p.n_parts = pl.n_parts;
   p.n_ctas = pl.grid_x;
+  if (push) p.push = *push;
 
   // one launch: the append (if asked for), the split-KV pass and the combine
   dim3 grid(pl.grid_x, sh.nkv, batch);
@@ -258,6 +267,30 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
   if (rc) return rc;
   SHARD_CHECK_LAUNCH();
   return SHARD_OK;
+}
+
+extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const ShardDecodeShape* shape_host,
+                                      const float* inv_freq, const float* codebook, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
+  return decode_attn_impl(seqs, batch, shape_host, inv_freq, codebook, workspace, workspace_bytes, nullptr, stream);
+}
+
+extern "C" int shard_b200_decode_attn_seqsplit(const ShardSeq* seq_host, const ShardDecodeShape* shape_host,
+                                               const float* inv_freq, const float* codebook, void* workspace,
+                                               size_t workspace_bytes, void* const* bufs_host, int32_t rank,
+                                               int32_t world, uint32_t epoch, void* stream) {
+  if (!bufs_host || world < 1 || world > PEER_MAX_WORLD || rank < 0 || rank >= world || epoch == 0 || !shape_host)
+    return SHARD_E_ARG;
+  if (!shape_host->partial_out) return SHARD_E_ARG;   // what travels is the unnormalised record
+  PeerPush push{};
+  for (int r = 0; r < world; ++r) {
+    if (!bufs_host[r]) return SHARD_E_ARG;
+    push.bufs[r] = reinterpret_cast<unsigned char*>(bufs_host[r]);
+  }
+  push.rank = rank;
+  push.world = world;
+  push.epoch = epoch;
+  return decode_attn_impl(seq_host, 1, shape_host, inv_freq, codebook, workspace, workspace_bytes, &push, stream);
 }
 
 extern "C" int shard_b200_lse_merge(const float* parts, int32_t n_parts, int32_t n_q, void* out_f16, void* stream) {
@@ -314,16 +347,38 @@ extern "C" int shard_b200_decode_attn_noalloc(const ShardSeq* seq_host, const Sh
   void* scratch = nullptr;
   rc = static_scratch_for_current_device(&scratch);
   if (rc != SHARD_OK) return rc;
-  // The array still holds whatever the previous call left there.  Only the header (status
-  // word and arrival counters) has to start at zero; every partial record is rewritten
-  // before it is read.
-  cudaError_t e = cudaMemsetAsync(scratch, 0, ws_header_bytes(1, shape_host->nkv), (cudaStream_t)stream);
+  // The array still holds whatever the previous call left there.  Only the arrival counters
+  // have to start at zero; every partial record is rewritten before it is read.  The status
+  // word in front of the counters is left alone: a launch that gave up leaves a 1 there, and
+  // it stays until shard_b200_decode_status(NULL, ...) has reported it.
+  cudaError_t e = cudaMemsetAsync((unsigned char*)scratch + WS_STATUS_BYTES, 0,
+                                  ws_header_bytes(1, shape_host->nkv) - WS_STATUS_BYTES, (cudaStream_t)stream);
   if (e != cudaSuccess) return (int)e;
   return shard_b200_decode_attn(seq_host, 1, shape_host, inv_freq, codebook, scratch,
                                 (size_t)SHARD_B200_STATIC_SCRATCH_BYTES, stream);
 }
 
-extern "C" int shard_b200_abi_version(void) { return 2; }
+extern "C" int shard_b200_decode_status(void* workspace, int32_t* status_host_out, void* stream) {
+  if (!status_host_out) return SHARD_E_ARG;
+  void* ws = workspace;
+  if (!ws) {
+    int rc = static_scratch_for_current_device(&ws);
+    if (rc != SHARD_OK) return rc;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  int32_t word = 0;
+  cudaError_t e = cudaMemcpyAsync(&word, ws, sizeof(word), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return (int)e;
+  if (word != 0) {
+    e = cudaMemsetAsync(ws, 0, sizeof(word), st);   // reported once; the next launch starts clean
+    if (e != cudaSuccess) return (int)e;
+  }
+  *status_host_out = word;
+  return SHARD_OK;
+}
+
+extern "C" int shard_b200_abi_version(void) { return 3; }
 
 extern "C" const char* shard_b200_status_string(int status) {
   switch (status) {

@@ -4,11 +4,20 @@
 #pragma once
 
 #include "common.cuh"
+#include "peer_layout.cuh"
 
 namespace shard {
 
 constexpr int ROWS_PER_CTA = 32;        // rows per CTA when a launch has no middle segment
 constexpr int MAX_ROW_CTAS = 18;
+
+// Sequence-split decode: where the launch's result goes when it is delivered straight into the
+// exchange buffers of all ranks (layout in peer_layout.cuh).  world == 0: no delivery.
+struct PeerPush {
+  unsigned char* bufs[PEER_MAX_WORLD];
+  int rank, world;
+  unsigned int epoch;
+};
 
 struct DecodeParams {
   ShardSeq one;
@@ -26,6 +35,7 @@ struct DecodeParams {
                         // themselves when there is a middle, else CTAs of their own; 0: no rows
   int n_parts;          // records per (sequence, query head): n_chunks rotated-space + n_row_parts standard
   int n_ctas;           // CTAs per (sequence, KV head) = gridDim.x
+  PeerPush push;        // sequence-split: deliver the combined record to every rank's exchange buffer
 };
 
 struct SoftmaxState {
@@ -272,8 +282,34 @@ __device__ __forceinline__ void ticket_combine(const DecodeParams& p, const Shar
     }
     v = v / SQRT_HD;
   }
-  if (!active) return;
   const float o = v + stdv;
+  if (p.push.world > 0) {
+    // Sequence-split decode: this CTA holds the rank's final record of four query heads.  It goes
+    // straight into slot epoch % 2 of EVERY rank's exchange buffer (plain peer stores over
+    // NVLink), then -- after a system-scope fence by every storing thread -- the epoch number is
+    // published in every rank's flag word for (this rank, this KV head).  The merge kernel of
+    // each rank waits for those flags.
+    const int slot = (int)(p.push.epoch & 1u);
+    const size_t flag_bytes = peer_flag_bytes(p.push.world, p.sh.nkv);
+    const size_t slot_floats = peer_slot_floats(p.push.world, p.sh.nkv);
+    if (active) {
+      for (int r = 0; r < p.push.world; ++r) {
+        float* rec = reinterpret_cast<float*>(p.push.bufs[r] + flag_bytes) + slot * slot_floats +
+                     ((size_t)p.push.rank * n_q + h) * PART;
+        if (d == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
+        rec[4 + d] = o;
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < p.push.world) {
+      volatile unsigned int* flag = reinterpret_cast<volatile unsigned int*>(p.push.bufs[tid]) +
+                                    ((size_t)slot * p.push.world + p.push.rank) * p.sh.nkv + kv;
+      *flag = p.push.epoch;
+    }
+    if (!sq.out) return;
+  }
+  if (!active) return;
   if (p.sh.partial_out) {
     float* rec = reinterpret_cast<float*>(sq.out) + (size_t)h * PART;
     if (d == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }

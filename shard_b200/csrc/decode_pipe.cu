@@ -32,6 +32,7 @@
 // Every hand-over is an mbarrier whose waiters see each of its phases; every wait is bounded and
 // raises the CTA's abort flag when it gives up, after which all roles drain, bulk copies in flight
 // are waited for, tensor memory is freed and the status word is set.
+#include <atomic>
 #include <cstdlib>
 
 #include "decode_common.cuh"
@@ -50,11 +51,7 @@ constexpr int PP_COL_S = 64;          // within a stage
 constexpr int PP_COL_O = 80;
 constexpr int PP_V_BYTES = 32768, PP_P_BYTES = 4096, PP_Q_BYTES = 4096, PP_CB_BYTES = 2048;
 constexpr int PP_ROWQ_BYTES = (GQA * HD + 256) * 4;   // queries as given + stream codebook, for the row path
-#ifdef SHARD_TC_DEBUG
-constexpr int PP_MISC_BYTES = 1024 + 1024 + 512;   // + per-role timing accumulators
-#else
 constexpr int PP_MISC_BYTES = 1024 + 1024;   // state + barriers, and slack for 1 KB alignment
-#endif
 
 // W holds R + 16 contraction positions (the last 16 carry the mean), in 64-position atoms of 16 KB
 __host__ __device__ constexpr int pp_w_bytes(int nw) { return ((32 * nw + 16 + 63) / 64) * 16384; }
@@ -99,18 +96,6 @@ __device__ __forceinline__ bool named_bar_or(int id, int count, bool flag) {
   return out != 0;
 }
 
-#ifdef SHARD_TC_DEBUG
-// development aid: per-CTA, per-role phase accounting (role 0: consumer warp 0, 1: unpack warp 12);
-// slot k accumulates the cycles that ended at stamp k
-__device__ long long* g_pp_debug = nullptr;
-#define PP_T0(role) long long pp_last__ = clock64(); \
-  long long* pp_rec__ = g_pp_debug ? reinterpret_cast<long long*>(smem + pp_smem_bytes(NW) - 1024 - 512) + 16 * (role) : nullptr
-#define PP_T(slot) do { if (pp_rec__ && lane == 0) { const long long n__ = clock64(); pp_rec__[(slot)] += n__ - pp_last__; pp_last__ = clock64(); } } while (0)
-extern "C" int shard_b200_pp_debug_set(long long* buf) { return (int)cudaMemcpyToSymbol(g_pp_debug, &buf, sizeof(buf)); }
-#else
-#define PP_T0(role) do {} while (0)
-#define PP_T(slot) do {} while (0)
-#endif
 
 template <int NW>  // rank / 32
 __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(const __grid_constant__ DecodeParams p) {
@@ -145,16 +130,6 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   float* rec_base = p.ws + (((size_t)blockIdx.z * p.n_parts + part) * sh.n_q + (size_t)kv * GQA) * PART;
 
-#ifdef SHARD_TC_DEBUG
-  const long long pp_kstart__ = clock64();
-  if (g_pp_debug && tid == 0) {
-    unsigned long long gt; unsigned smid;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
-    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
-    g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 50] = (long long)gt;
-    g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 52] = smid;
-  }
-#endif
   const int n_rows = sh.n_sink + sh.n_win + sh.n_dec + sh.n_stream;
   // the CTA that owns the newest streamed row quantises it before anybody reads the stream
   const bool append_here = sh.append && p.n_row_parts > 0 && (n_rows - 1) % p.n_row_parts == part;
@@ -254,10 +229,6 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     uint4* z = reinterpret_cast<uint4*>(p_s);
     for (int i = tid; i < (PP_STAGES * PP_P_BYTES) / 16; i += PP_THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
   }
-#ifdef SHARD_TC_DEBUG
-  if (tid < 48) reinterpret_cast<long long*>(smem + pp_smem_bytes(NW) - 1024 - 512)[tid] = 0;
-  if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 36] = clock64() - pp_kstart__;
-#endif
   // Up to here only tensors that no decode call ever writes were touched (weights, coefficients,
   // V codes, codebooks).  The query, the new token, the stream rows, the phase table, the scratch
   // and the output may come from, or still be in use by, the call before this one.
@@ -291,9 +262,6 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-#ifdef SHARD_TC_DEBUG
-  if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 48] += clock64() - pp_kstart__;
-#endif
 
   float acc[16];
 #pragma unroll
@@ -346,23 +314,8 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       return true;
     };
 
-#ifdef SHARD_TC_DEBUG
-    if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 40] = clock64() - pp_kstart__;
-#endif
-    PP_T0(0);
-#ifdef SHARD_TC_DEBUG
-    if (warp != 0) pp_rec__ = nullptr;
-    if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 41] = clock64() - pp_kstart__;
-#endif
-
     bool bad = false;
-#ifdef SHARD_TC_DEBUG
-    if (g_pp_debug && issuer && g == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 44] = clock64() - pp_kstart__;
-#endif
     if (issuer && g < n_my) bad |= !issue_mma1(g);
-#ifdef SHARD_TC_DEBUG
-    if (g_pp_debug && issuer && g == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 45] = clock64() - pp_kstart__;
-#endif
     __syncwarp();
     // Fused append: in the CTA that owns the newest streamed row, two warps of the last consumer
     // group -- whose first tile is the furthest away -- quantise the new token now.  The row is
@@ -385,15 +338,8 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       pc[0] = prow[0 * 32]; ps[0] = prow[8 * 32];
       pc[1] = prow[1 * 32]; ps[1] = prow[9 * 32];
       pc[2] = prow[2 * 32]; ps[2] = prow[10 * 32];
-
-      PP_T(0);
       bad |= !mbar_wait(KN_FULL(g), par, abort_s);
       tc_fence_after();
-      PP_T(1);
-#ifdef SHARD_TC_DEBUG
-      if (g_pp_debug && tid == 0 && it == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 46] = clock64() - pp_kstart__;
-      if (g_pp_debug && tid == 0 && it == 3) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 47] = clock64() - pp_kstart__;
-#endif
 
       // ---- rotate: 8 chunks of 8 pairs; K~ goes back in place --------------------------------
       // chunk ch reads c columns [8ch, 8ch+8) and d columns [64+8ch, ...) and writes 4 columns of c'
@@ -406,9 +352,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
         if (ch + 3 < 8) { pc[ch + 3] = prow[(ch + 3) * 32]; ps[ch + 3] = prow[(8 + ch + 3) * 32]; }
         const uint32_t cos2[4] = {pc[ch].x, pc[ch].y, pc[ch].z, pc[ch].w};
         const uint32_t sin2[4] = {ps[ch].x, ps[ch].y, ps[ch].z, ps[ch].w};
-        PP_T(13);
         tmem_wait_ld();
-        PP_T(14);
         uint32_t oc[4], od[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -421,9 +365,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
         tmem_st_x4(lane_T + 8 * ch, oc);
         tmem_st_x4(lane_T + 8 * ch + 4, od);
       }
-      PP_T(2);
       tmem_wait_st();
-      PP_T(9);
       tc_fence_before();
       bad = named_bar_or(1 + g, 128, bad || *abort_s);
       if (bad) break;                                   // uniform over the group
@@ -436,7 +378,6 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
         umma_commit_1t(S_FULL(g));
       }
       __syncwarp();
-      PP_T(3);
       // (while the tensor core computes the scores)
       // ---- gather the token's V row (32 codes) into the stage's V tile -------------------------
       bad |= !mbar_wait(V_FULL(g), par, abort_s);
@@ -450,12 +391,10 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
           *reinterpret_cast<uint4*>(v_g + (j >> 3) * 16384 + sw128_off(m, j & 7)) = make_uint4(e0.x, e0.y, e1.x, e1.y);
         }
       }
-      PP_T(8);
 
       // ---- softmax over this warp's 32 tokens ---------------------------------------------------
       bad |= !mbar_wait(S_FULL(g), par, abort_s);
       tc_fence_after();
-      PP_T(4);
       {
         uint32_t sraw[4];
         tmem_ld_x4(lane_T + PP_COL_S, sraw);
@@ -474,9 +413,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
           if (lane == 0) alpha_g[n] = al;
         }
       }
-      PP_T(11);
       fence_proxy_async();
-      PP_T(12);
       tc_fence_before();
       bad = named_bar_or(1 + g, 128, bad || *abort_s);
       if (bad) break;                                   // uniform over the group
@@ -490,12 +427,10 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
         umma_commit_1t(O_FULL(g));
       }
       __syncwarp();
-      PP_T(5);
 
       // ---- accumulate channel m of the tile's P.V ------------------------------------------------
       bad |= !mbar_wait(O_FULL(g), par, abort_s);
       tc_fence_after();
-      PP_T(6);
       {
         uint32_t o[16];
         tmem_ld_x16(lane_T + PP_COL_O, o);
@@ -514,12 +449,8 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       if (lane == 0) mbar_arrive(T_EMPTY(g));
       if (issuer && it + PP_STAGES < n_my) bad |= !issue_mma1(it + PP_STAGES);
       __syncwarp();
-      PP_T(7);
     }
     // giving up: do not leave while a copy this thread asked for may still be landing
-#ifdef SHARD_TC_DEBUG
-    if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 42] = clock64() - pp_kstart__;
-#endif
     if ((bad || *abort_s) && issuer && vc_issued > 0)
       mbar_wait(V_FULL(g), (uint32_t)((vc_issued - 1) & 1), abort_s);
   } else {
@@ -532,10 +463,6 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       const uint32_t ones[8] = {0x00003C00u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
       tmem_st_x8(lane_A + R / 2, ones);
     }
-    PP_T0(1);
-#ifdef SHARD_TC_DEBUG
-    if (warp != PP_UNPACK_WARP0) pp_rec__ = nullptr;
-#endif
     bool bad = false;
     for (int it = 0; it < n_my && !bad; ++it) {
       bad = !mbar_wait(C_FULL(it & 1), (uint32_t)((it >> 1) & 1), abort_s);
@@ -547,7 +474,6 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
         bad = __any_sync(0xffffffffu, bad || *abort_s);
         if (bad) break;                                 // uniform over the warp
         tc_fence_after();
-        PP_T(0);
 #pragma unroll
         for (int i = 2 * j; i < 2 * j + 2 && i < NW; ++i) {
           const uint4 xi = row[i];
@@ -563,24 +489,20 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
           }
           tmem_st_x16(lane_A + 16 * i, o);
         }
-        PP_T(1);
       }
       if (bad) break;
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(A_FULL(it % PP_STAGES));   // this warp's rows are in place, its reads of c_s done
-      PP_T(2);
     }
     // The unpack warps run about three tiles ahead of the consumers.  In that slack they take this
     // CTA's share of the fp16 / streamed rows (row u belongs to CTA u % n_row_parts), one warp per
     // row.  The rows get a record of their own: standard V space, while the middle's record is in rotated space.
     // The coefficient staging buffers are free by now and serve as merge scratch.
     bad = named_bar_or(4, 128, bad || *abort_s);
-    PP_T(3);
     if (!bad && p.n_row_parts > 0) {
       if (append_here) bad = !mbar_wait(APPEND_DONE, 0u, abort_s);
-      PP_T(4);
       SoftmaxState st;
       softmax_init(st);
       process_rows(st, sq, sh, kv, part + p.n_row_parts * quad, p.n_row_parts * 4, qr_s, cbs_s, lane);
@@ -588,7 +510,6 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       partial_store<4>(st, scratch, quad, lane);
       named_bar_sync(4, 128);
       partial_merge<4>(scratch, rec_rows, m);
-      PP_T(5);
     }
   }
 
@@ -638,20 +559,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   tc_fence_before();
   __syncthreads();
   if (warp == PP_UNPACK_WARP0) tmem_dealloc(tmem_base, PP_TMEM_COLS);
-#ifdef SHARD_TC_DEBUG
-  if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 43] = clock64() - pp_kstart__;
-#endif
   ticket_combine<PP_THREADS>(p, sq, kv, blockIdx.z, reinterpret_cast<float*>(w_s), tid, true);
-#ifdef SHARD_TC_DEBUG
-  if (g_pp_debug && tid == 0) g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 49] += clock64() - pp_kstart__;
-  if (g_pp_debug && tid == 0) {
-    unsigned long long gt;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
-    g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + 51] = (long long)gt;
-  }
-  if (g_pp_debug && tid < 48)
-    g_pp_debug[64 * (blockIdx.x + gridDim.x * blockIdx.y) + tid] += reinterpret_cast<long long*>(smem + pp_smem_bytes(NW) - 1024 - 512)[tid];
-#endif
 }
 
 // Prepared weights: per KV head, W = basis * coefficient scale as fp16 in the K-major, 128-byte
@@ -698,21 +606,28 @@ template <int NW>
 static int launch_pipe_one(const DecodeParams& p, dim3 grid, cudaStream_t st) {
   constexpr int SMEM = pp_smem_bytes(NW);
   static_assert(SMEM >= (2 * GQA * HD + 256 + PP_WARPS * GQA * 130) * 4, "row path scratch must fit");
-  static bool configured = false;
-  if (!configured) {
+  // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel
+  static std::atomic<bool> configured[MAX_DEVICES];
+  int dev = -1;
+  cudaError_t de = cudaGetDevice(&dev);
+  if (de != cudaSuccess) return (int)de;
+  if (dev < 0 || dev >= MAX_DEVICES) return SHARD_E_ARG;
+  if (!configured[dev].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(decode_partial_pipe_kernel<NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured[dev].store(true, std::memory_order_release);
   }
-  // Programmatic dependent launch: when the kernel in front of this one in the stream is another
-  // decode launch, this one's CTAs move onto SMs as that one's CTAs retire and set up (barriers,
-  // first bulk copies) while its last CTAs finish; griddep_wait in the kernel keeps the order of
-  // everything that matters.  SHARD_B200_PDL=0 in the environment turns it off.
-  static int use_pdl = -1;
-  if (use_pdl < 0) {
+  // Programmatic dependent launch: this launch's CTAs may move onto SMs and run their set-up
+  // (barriers, first bulk copies of tensors that no decode call writes) while the kernel in front
+  // of it in the stream is still finishing; griddep_wait in the kernel keeps the order of
+  // everything else.  Off for a call with shape.no_overlap, or for all calls with
+  // SHARD_B200_PDL=0 in the environment.
+  static int use_pdl_env = -1;
+  if (use_pdl_env < 0) {
     const char* e = getenv("SHARD_B200_PDL");
-    use_pdl = (e && e[0] == '0') ? 0 : 1;
+    use_pdl_env = (e && e[0] == '0') ? 0 : 1;
   }
+  const int use_pdl = use_pdl_env && !p.sh.no_overlap;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(PP_THREADS);

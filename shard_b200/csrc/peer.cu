@@ -2,29 +2,51 @@
 // their log-sum-exp merge, in one kernel.
 //
 // Every rank owns one exchange buffer (plain cudaMalloc memory, opened by the other ranks of
-// the node through CUDA IPC).  Layout, identical on all ranks:
+// the node through CUDA IPC; layout in peer_layout.cuh).  Per layer-step and rank:
 //
-//   flags [2 slots][world][nkv] u32      "rank r has delivered its records of epoch e for KV head kv"
-//   parts [2 slots][world][n_q][132] f32 rank r's (max, sum-exp, 0, 0, acc[128]) per query head
+//   (1) this rank's four records per KV head go into slot e % 2 of EVERY rank's buffer with plain
+//       peer stores,
+//   (2) system-scope fence, then the epoch number is published in every rank's flag word,
+//   (3) wait -- bounded by the global timer -- until all `world` flag words of the own buffer show
+//       the epoch,
+//   (4) merge the `world` records of the own buffer in rank order: same operations and order as
+//       decode_combine_kernel, so every rank gets bit-identical output.
 //
-// One launch per layer-step and rank, grid = nkv CTAs (CTA kv handles that KV head's four query
-// heads): (1) store this rank's four records into slot e % 2 of EVERY rank's buffer with plain
-// peer stores, (2) system-scope fence, then publish the epoch number in every rank's flag word,
-// (3) wait -- bounded -- until all `world` flag words of the own buffer show the epoch,
-// (4) merge the `world` records of the own buffer in rank order: same operations and order as
-// decode_combine_kernel, so every rank gets bit-identical output.
-//
-// Two slots suffice: a rank can only be writing epoch e + 2 after every rank has published
-// e + 1, i.e. after every rank has finished reading epoch e (same slot) in stream order.
+// seqsplit_exchange_merge_kernel does (1)-(4) for a record that lies in this rank's memory.
+// seqsplit_wait_merge_kernel does (3)-(4) only: (1)-(2) were done by the decode launch itself
+// (the CTA that combines a KV head's split-KV records delivers the result, decode_common.cuh).
+// It is launched with programmatic stream serialization, so it is resident and polling while
+// the decode launch in front of it still runs, and the merge starts the moment the last flag lands.
 // No multicast, no multimem: plain loads and stores on peer pointers.
 #include <cstring>
 
-#include "common.cuh"
+#include "peer_layout.cuh"
+#include "tcgen05.cuh"
 
 namespace shard {
 
-constexpr int PEER_MAX_WORLD = 16;
-constexpr long long PEER_WAIT_SPINS = 4000000;   // x ~50 ns: gives up after roughly 0.2 s
+constexpr unsigned long long PEER_DEFAULT_WAIT_NS = 200ull * 1000 * 1000;   // 0.2 s
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Waits until *flag == epoch or `limit_ns` nanoseconds have passed; false on time-out.
+__device__ __forceinline__ bool wait_epoch(volatile unsigned int* flag, unsigned int epoch,
+                                           unsigned long long limit_ns) {
+  if (*flag == epoch) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (*flag == epoch) return true;
+      __nanosleep(32);
+    }
+    if (global_timer_ns() - t0 > limit_ns) return false;
+  }
+}
 
 struct PeerParams {
   unsigned char* bufs[PEER_MAX_WORLD];   // exchange buffer of every rank (own entry = local pointer)
@@ -33,12 +55,29 @@ struct PeerParams {
   int* status;                           // set to 1 when the bounded wait gave up (may be null)
   int rank, world, nkv;
   unsigned int epoch;
+  unsigned long long wait_ns;            // bound of the flag wait
 };
 
-__host__ __device__ inline size_t peer_flag_bytes(int world, int nkv) {
-  return ((size_t)2 * world * nkv * sizeof(unsigned int) + 255) & ~(size_t)255;
+// (4): merge of the `world` records of KV head kv in the own buffer, in rank order
+__device__ __forceinline__ void merge_own_buffer(const PeerParams& p, int kv, int tid, int slot) {
+  const int n_q = p.nkv * GQA;
+  const size_t flag_bytes = peer_flag_bytes(p.world, p.nkv);
+  const size_t slot_floats = peer_slot_floats(p.world, p.nkv);
+  const int h = kv * GQA + (tid >> 7), d = tid & (HD - 1);
+  const float* base = reinterpret_cast<const float*>(p.bufs[p.rank] + flag_bytes) + slot * slot_floats + (size_t)h * PART;
+  const size_t pstride = (size_t)n_q * PART;
+  float M = neg_inf();
+  for (int r = 0; r < p.world; ++r) M = fmaxf(M, __ldcg(base + r * pstride));
+  float L = 0.f, acc = 0.f;
+  for (int r = 0; r < p.world; ++r) {
+    const float* rec = base + r * pstride;
+    const float m = __ldcg(rec);
+    const float wt = (m == neg_inf()) ? 0.f : exp2f((m - M) * LOG2E);
+    L = fmaf(wt, __ldcg(rec + 1), L);
+    acc = fmaf(wt, __ldcg(rec + 4 + d), acc);
+  }
+  reinterpret_cast<__half*>(p.out)[(size_t)h * HD + d] = __float2half_rn(acc / L);
 }
-__host__ __device__ inline size_t peer_slot_floats(int world, int nkv) { return (size_t)world * nkv * GQA * PART; }
 
 __global__ void __launch_bounds__(GQA* HD) seqsplit_exchange_merge_kernel(const __grid_constant__ PeerParams p) {
   __shared__ int timed_out;
@@ -69,11 +108,7 @@ __global__ void __launch_bounds__(GQA* HD) seqsplit_exchange_merge_kernel(const 
   if (tid < p.world) {
     volatile unsigned int* flag =
         reinterpret_cast<volatile unsigned int*>(p.bufs[p.rank]) + ((size_t)slot * p.world + tid) * p.nkv + kv;
-    long long spins = 0;
-    while (*flag != p.epoch) {
-      if (++spins > PEER_WAIT_SPINS) { timed_out = 1; break; }
-      __nanosleep(40);
-    }
+    if (!wait_epoch(flag, p.epoch, p.wait_ns)) timed_out = 1;
     __threadfence_system();
   }
   __syncthreads();
@@ -81,21 +116,32 @@ __global__ void __launch_bounds__(GQA* HD) seqsplit_exchange_merge_kernel(const 
     if (tid == 0 && p.status) atomicExch(p.status, 1);
     return;
   }
-  // (4) merge in rank order; all partial records are in standard V space
-  const int h = kv * GQA + (tid >> 7), d = tid & (HD - 1);
-  const float* base = reinterpret_cast<const float*>(p.bufs[p.rank] + flag_bytes) + slot * slot_floats + (size_t)h * PART;
-  const size_t pstride = (size_t)n_q * PART;
-  float M = neg_inf();
-  for (int r = 0; r < p.world; ++r) M = fmaxf(M, __ldcg(base + r * pstride));
-  float L = 0.f, acc = 0.f;
-  for (int r = 0; r < p.world; ++r) {
-    const float* rec = base + r * pstride;
-    const float m = __ldcg(rec);
-    const float wt = (m == neg_inf()) ? 0.f : exp2f((m - M) * LOG2E);
-    L = fmaf(wt, __ldcg(rec + 1), L);
-    acc = fmaf(wt, __ldcg(rec + 4 + d), acc);
+  merge_own_buffer(p, kv, tid, slot);
+}
+
+// Steps (3)-(4) for records that the decode launch in front of this kernel delivers itself.
+__global__ void __launch_bounds__(GQA* HD) seqsplit_wait_merge_kernel(const __grid_constant__ PeerParams p) {
+  __shared__ int timed_out;
+  const int kv = blockIdx.x, tid = threadIdx.x;
+  const int slot = (int)(p.epoch & 1u);
+  griddep_launch();
+  if (tid == 0) timed_out = 0;
+  __syncthreads();
+  if (tid < p.world) {
+    volatile unsigned int* flag =
+        reinterpret_cast<volatile unsigned int*>(p.bufs[p.rank]) + ((size_t)slot * p.world + tid) * p.nkv + kv;
+    if (!wait_epoch(flag, p.epoch, p.wait_ns)) timed_out = 1;
+    __threadfence_system();
   }
-  reinterpret_cast<__half*>(p.out)[(size_t)h * HD + d] = __float2half_rn(acc / L);
+  __syncthreads();
+  // everything in front of this kernel in the stream has finished (whoever follows this kernel
+  // with a programmatic launch of its own relies on that, also when the wait above gave up)
+  griddep_wait();
+  if (timed_out) {
+    if (tid == 0 && p.status) atomicExch(p.status, 1);
+    return;
+  }
+  merge_own_buffer(p, kv, tid, slot);
 }
 
 }  // namespace shard
@@ -141,25 +187,54 @@ extern "C" int shard_b200_peer_free(void* ptr) {
   return e == cudaSuccess ? SHARD_OK : (int)e;
 }
 
-extern "C" int shard_b200_seqsplit_merge(const float* my_part, void* const* bufs_host, int32_t rank, int32_t world,
-                                         int32_t nkv, uint32_t epoch, void* out_f16, int* status_dev, void* stream) {
-  if (!my_part || !bufs_host || !out_f16 || world < 1 || world > PEER_MAX_WORLD || rank < 0 || rank >= world ||
-      nkv < 1 || epoch == 0)
+static int fill_peer_params(PeerParams& p, void* const* bufs_host, int32_t rank, int32_t world, int32_t nkv,
+                            uint32_t epoch, void* out_f16, int* status_dev, uint32_t timeout_us) {
+  if (!bufs_host || !out_f16 || world < 1 || world > PEER_MAX_WORLD || rank < 0 || rank >= world || nkv < 1 ||
+      epoch == 0)
     return SHARD_E_ARG;
-  if ((uintptr_t)my_part & 15) return SHARD_E_ALIGN;
-  PeerParams p{};
   for (int r = 0; r < world; ++r) {
     if (!bufs_host[r]) return SHARD_E_ARG;
     p.bufs[r] = reinterpret_cast<unsigned char*>(bufs_host[r]);
   }
-  p.my_part = my_part;
   p.out = out_f16;
   p.status = status_dev;
   p.rank = rank;
   p.world = world;
   p.nkv = nkv;
   p.epoch = epoch;
+  p.wait_ns = timeout_us ? (unsigned long long)timeout_us * 1000ull : PEER_DEFAULT_WAIT_NS;
+  return SHARD_OK;
+}
+
+extern "C" int shard_b200_seqsplit_merge(const float* my_part, void* const* bufs_host, int32_t rank, int32_t world,
+                                         int32_t nkv, uint32_t epoch, void* out_f16, int* status_dev,
+                                         uint32_t timeout_us, void* stream) {
+  if (!my_part) return SHARD_E_ARG;
+  if ((uintptr_t)my_part & 15) return SHARD_E_ALIGN;
+  PeerParams p{};
+  int rc = fill_peer_params(p, bufs_host, rank, world, nkv, epoch, out_f16, status_dev, timeout_us);
+  if (rc != SHARD_OK) return rc;
+  p.my_part = my_part;
   seqsplit_exchange_merge_kernel<<<nkv, GQA * HD, 0, (cudaStream_t)stream>>>(p);
   SHARD_CHECK_LAUNCH();
   return SHARD_OK;
+}
+
+extern "C" int shard_b200_seqsplit_wait_merge(void* const* bufs_host, int32_t rank, int32_t world, int32_t nkv,
+                                              uint32_t epoch, void* out_f16, int* status_dev, uint32_t timeout_us,
+                                              void* stream) {
+  PeerParams p{};
+  int rc = fill_peer_params(p, bufs_host, rank, world, nkv, epoch, out_f16, status_dev, timeout_us);
+  if (rc != SHARD_OK) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nkv);
+  cfg.blockDim = dim3(GQA * HD);
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, seqsplit_wait_merge_kernel, p);
+  return e == cudaSuccess ? SHARD_OK : (int)e;
 }

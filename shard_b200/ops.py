@@ -213,6 +213,21 @@ def decode_attn(seq_or_table, batch, shape, inv_freq, codebook, workspace):
         check(rc, "decode_attn")
 
 
+def decode_status(workspace=None):
+    """Status word of the decode launches that used `workspace` (None: the library's built-in
+    scratch on the current device): 0, or 1 if a bounded in-kernel wait gave up.  Waits for the
+    current stream and clears a set word."""
+    word = C.c_int32(0)
+    check(_lib.load().shard_b200_decode_status(None if workspace is None else workspace.data_ptr(),
+                                               C.byref(word), cur_stream()), "decode_status")
+    return int(word.value)
+
+
+def decode_status_check(workspace=None):
+    if decode_status(workspace) != 0:
+        raise _lib.ShardError("a decode launch gave up on a bounded in-kernel wait; its output is undefined")
+
+
 def lse_merge(parts, out=None):
     """parts: (n_parts, n_q, 132) fp32 -> (n_q, 128) fp16."""
     require_cuda(parts)

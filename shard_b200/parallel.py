@@ -9,7 +9,9 @@ tensor dictionary as the unit of work.
 * sequence-split: one long sequence's compressed middle is cut into contiguous
   token ranges, one per rank.  Every rank runs the fused decode on its range and
   emits per query head (max, sum-exp, acc[128]); the records (16.9 KB per rank and
-  layer) are all-gathered over NCCL and combined with the same log-sum-exp kernel
+  layer) travel over NVLink peer memory -- delivered by the decode launch itself and
+  merged by a kernel that is already polling (`PeerExchange`) -- or, without peer
+  access, are all-gathered over NCCL and combined with the same log-sum-exp kernel
   that merges the split-KV partials inside one GPU.  Rank 0 also owns the fp16
   sink/window and the streamed tokens.
 """
@@ -21,7 +23,7 @@ import torch.distributed as dist
 from . import _lib, ops
 from ._lib import ShardSeq, ptr
 
-TOKEN_ALIGN = 16  # decode tiles are 16 tokens; ranges start on tile boundaries
+TOKEN_ALIGN = 128  # decode tiles are 128 tokens; ranges start on tile boundaries
 
 
 def split_ranges(n_comp: int, world: int, align: int = TOKEN_ALIGN):
@@ -95,9 +97,10 @@ class PeerExchange:
     NCCL all-gather followed by a merge launch.  All ranks must call `merge` the same number of
     times, in the same order.  Needs every rank on its own GPU of one node with peer access."""
 
-    def __init__(self, nkv: int, group=None, device=None):
+    def __init__(self, nkv: int, group=None, device=None, timeout_us: int = 0):
         import ctypes as C
         self.group = group
+        self.timeout_us = int(timeout_us)      # bound of the in-kernel flag wait; 0 = library default (0.2 s)
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.nkv = nkv
         self.dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
@@ -136,7 +139,28 @@ class PeerExchange:
         self.epoch += 1
         _lib.check(_lib.load().shard_b200_seqsplit_merge(part.data_ptr(), self._ptrs, self.rank, self.world, self.nkv,
                                                          self.epoch, out.data_ptr(), self.status.data_ptr(),
-                                                         _lib.cur_stream()), "seqsplit_merge")
+                                                         self.timeout_us, _lib.cur_stream()), "seqsplit_merge")
+        return out
+
+    # -- fused form: the decode launch delivers, a polling kernel merges -----------------------
+    def launch_decode(self, seq, shape, inv_ptr, cb_ptr, ws):
+        """Called by `decode_layer(..., push=self)`: the decode launch of the NEXT epoch, whose
+        combining CTAs store the rank's record into every rank's buffer and publish the epoch."""
+        import ctypes as C
+        _lib.check(_lib.load().shard_b200_decode_attn_seqsplit(
+            C.addressof(seq), C.byref(shape), inv_ptr, cb_ptr, ws.data_ptr(), ws.numel() * ws.element_size(),
+            self._ptrs, self.rank, self.world, self.epoch + 1, _lib.cur_stream()), "decode_attn_seqsplit")
+
+    def wait_merge(self, out: torch.Tensor | None = None):
+        """Wait for every rank's record of the epoch `launch_decode` delivered and merge them."""
+        n_q = 4 * self.nkv
+        if out is None:
+            out = torch.empty(n_q, 128, dtype=torch.float16, device=self.dev)
+        self.epoch += 1
+        _lib.check(_lib.load().shard_b200_seqsplit_wait_merge(self._ptrs, self.rank, self.world, self.nkv, self.epoch,
+                                                              out.data_ptr(), self.status.data_ptr(),
+                                                              self.timeout_us, _lib.cur_stream()),
+                   "seqsplit_wait_merge")
         return out
 
     def check(self):
@@ -156,28 +180,56 @@ class PeerExchange:
             self._own = None
 
 
-def seqsplit_decode(q_rope, layer, pos_q, group=None, gather_buf=None, timing=None, peer=None):
+def neutral_partial(n_q: int, device):
+    """The record of a rank that has nothing to attend to: max = -inf, sum-exp = 0, acc = 0.
+    Every merge gives it weight zero."""
+    part = torch.zeros(n_q, _lib.PART_STRIDE, dtype=torch.float32, device=device)
+    part[:, 0] = float("-inf")
+    return part
+
+
+def seqsplit_decode(q_rope, layer, pos_q, group=None, gather_buf=None, timing=None, peer=None, out=None,
+                    part_buf=None):
     """Sequence-split decode of one layer whose dictionary was cut by `shard_layer_tokens`.
 
     Every rank calls this with the same query; all ranks return the same
     (1, n_q, 1, hd) fp16 tensor (the combine runs in fixed rank order).  With `peer`
-    (a `PeerExchange`) the records travel over NVLink peer memory inside the merge kernel;
-    without it through an NCCL all-gather followed by `lse_merge`.
+    (a `PeerExchange`) the decode launch delivers its record into every rank's exchange
+    buffer over NVLink and a merge kernel that is already polling finishes the step;
+    without it the records go through an NCCL all-gather followed by `lse_merge`.
+    A rank whose range is empty (fewer tiles than ranks) and that owns no fp16 / streamed
+    rows launches no decode and contributes the neutral record.
     `timing`, if given, is a dict receiving CUDA events around the merge step.
     """
     from .attention import decode_layer
     rank = dist.get_rank(group)
-    part = decode_layer(q_rope, layer, pos_q, partial_out=True, with_fp16_segments=(rank == 0))
-    if timing is not None:
-        timing["merge_start"].record()
-    if peer is not None:
-        out = peer.merge(part)
+    gc = layer._gpu_compressed
+    n_q = q_rope.shape[1]
+    first = rank == 0
+    n_rows = 0
+    if first:
+        n_rows = gc["sink_k"].shape[2] + gc["win_k"].shape[2] + gc.get("stream_n", 0)
+        n_rows += gc["decode_k"].shape[2] if "decode_k" in gc else 0
+    idle = gc["n_compress"] == 0 and n_rows == 0
+    out2 = None if out is None else out.view(n_q, q_rope.shape[3])
+    if peer is not None and not idle:
+        decode_layer(q_rope, layer, pos_q, partial_out=True, with_fp16_segments=first, out=part_buf, push=peer)
+        if timing is not None:
+            timing["merge_start"].record()
+        res = peer.wait_merge(out2)
     else:
-        parts = all_gather_partials(part, group, gather_buf)
-        out = ops.lse_merge(parts)
+        part = (neutral_partial(n_q, q_rope.device) if idle else
+                decode_layer(q_rope, layer, pos_q, partial_out=True, with_fp16_segments=first, out=part_buf))
+        if timing is not None:
+            timing["merge_start"].record()
+        if peer is not None:
+            res = peer.merge(part, out2)
+        else:
+            parts = all_gather_partials(part, group, gather_buf)
+            res = ops.lse_merge(parts, out2)
     if timing is not None:
         timing["merge_end"].record()
-    return out.view(1, q_rope.shape[1], 1, q_rope.shape[3])
+    return res.view(1, n_q, 1, q_rope.shape[3])
 
 
 class BatchedDecoder:
@@ -274,3 +326,8 @@ class BatchedDecoder:
                        "decode_attn")
         self.n_stream += 1
         return self.out
+
+    def check(self):
+        """Raise `ShardError` if a launch of this decoder gave up on a bounded in-kernel wait since
+        the last check.  Waits for the current stream: once per step or request, not per layer."""
+        ops.decode_status_check(self.ws)

@@ -67,35 +67,40 @@ def make_token(seed: int, device="cpu", nkv: int = N_KV, n_q: int = N_Q, hd: int
 
 
 def random_compressed_layer(n_comp, device, seed, compress_start=4, n_sink=4, n_win=64, rank=192, nkv=N_KV,
-                            hd=HEAD_DIM):
+                            hd=HEAD_DIM, gen_device=None):
     """A compressed layer with random codes, built directly on `device` (no prefill, no
     compression).  Decode cost does not depend on code values, so the multi-GPU
     benchmark workloads use this to set up many / very long caches quickly.  Returns the
-    per-layer tensor dictionary in the product's format (kernel-side weights attached)."""
-    from .cache import attach_kernel_format
+    per-layer tensor dictionary in the product's format (kernel-side weights attached).
+    With `gen_device="cpu"` the values are drawn by the CPU generator and then moved, which
+    makes them identical on every rank whatever GPU it runs on."""
+    from shard_b200.cache import attach_kernel_format
     dev = torch.device(device)
-    g = torch.Generator(device=dev).manual_seed(seed)
+    gdev = dev if gen_device is None else torch.device(gen_device)
+    g = torch.Generator(device=gdev).manual_seed(seed)
     p = nkv * hd
-    basis_q = torch.randint(-127, 128, (p, rank), generator=g, device=dev, dtype=torch.int8)
-    basis_scale = (0.08 / 127 * (0.5 + torch.rand(rank, generator=g, device=dev))).half()
-    decay = torch.exp(-0.01 * torch.arange(rank, device=dev, dtype=torch.float32))
+    basis_q = torch.randint(-127, 128, (p, rank), generator=g, device=gdev, dtype=torch.int8)
+    basis_scale = (0.08 / 127 * (0.5 + torch.rand(rank, generator=g, device=gdev))).half()
+    decay = torch.exp(-0.01 * torch.arange(rank, device=gdev, dtype=torch.float32))
     gc = {
-        "k_coeffs": torch.randint(0, 256, (n_comp * rank // 2,), generator=g, device=dev, dtype=torch.uint8),
+        "k_coeffs": torch.randint(0, 256, (n_comp * rank // 2,), generator=g, device=gdev, dtype=torch.uint8),
         "k_coeff_scale": (decay * 0.4).half(),
         "k_coeffs_shape": (n_comp, rank),
         "k_basis_q": basis_q,
         "k_basis_scale": basis_scale,
         "k_basis_f16": (basis_q.half() * basis_scale).contiguous(),
-        "k_mean": (torch.randn(p, generator=g, device=dev) * 0.1).half(),
-        "v_indices_u8": torch.randint(0, 256, (nkv, n_comp, hd // 4), generator=g, device=dev, dtype=torch.uint8),
-        "v_centroids_f16": (torch.randn(256, 4, generator=g, device=dev) * 0.4).half(),
-        "v_ch_f16": (0.5 + 3 * torch.rand(nkv, hd, generator=g, device=dev)).half(),
-        "sink_k": torch.randn(1, nkv, n_sink, hd, generator=g, device=dev).half(),
-        "sink_v": torch.randn(1, nkv, n_sink, hd, generator=g, device=dev).half(),
-        "win_k": torch.randn(1, nkv, n_win, hd, generator=g, device=dev).half(),
-        "win_v": torch.randn(1, nkv, n_win, hd, generator=g, device=dev).half(),
+        "k_mean": (torch.randn(p, generator=g, device=gdev) * 0.1).half(),
+        "v_indices_u8": torch.randint(0, 256, (nkv, n_comp, hd // 4), generator=g, device=gdev, dtype=torch.uint8),
+        "v_centroids_f16": (torch.randn(256, 4, generator=g, device=gdev) * 0.4).half(),
+        "v_ch_f16": (0.5 + 3 * torch.rand(nkv, hd, generator=g, device=gdev)).half(),
+        "sink_k": torch.randn(1, nkv, n_sink, hd, generator=g, device=gdev).half(),
+        "sink_v": torch.randn(1, nkv, n_sink, hd, generator=g, device=gdev).half(),
+        "win_k": torch.randn(1, nkv, n_win, hd, generator=g, device=gdev).half(),
+        "win_v": torch.randn(1, nkv, n_win, hd, generator=g, device=gdev).half(),
         "n_compress": n_comp, "batch": 1, "compress_start": compress_start,
     }
+    if gdev != dev:
+        gc = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in gc.items()}
     gc["k_mean_f16"] = gc["k_mean"]
     gc["v_packed"] = gc["v_indices_u8"].view(-1)
     attach_kernel_format(gc, nkv)
@@ -104,7 +109,7 @@ def random_compressed_layer(n_comp, device, seed, compress_start=4, n_sink=4, n_
 
 def random_cache(n_comp, layers, device, seed0, **kw):
     """A `Cache` whose layers are `random_compressed_layer`s (already 'compressed')."""
-    from .cache import Cache
+    from shard_b200.cache import Cache
     cache = Cache(num_layers=layers, rope_inv_freq=rope_inv_freq(), device=str(device))
     cache._streaming = True
     cache._compressed = True

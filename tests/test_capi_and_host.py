@@ -28,7 +28,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), name
     assert sorted(_lib.symbols()) == declared
-    assert lib.shard_b200_abi_version() >= 1
+    assert lib.shard_b200_abi_version() == 3
     assert lib.shard_b200_status_string(-1).decode().startswith("invalid argument")
 
 
@@ -36,7 +36,7 @@ def test_struct_layouts_match_header():
     import ctypes as C
     from shard_b200 import _lib
     assert C.sizeof(_lib.ShardSeq) == 21 * 8
-    assert C.sizeof(_lib.ShardDecodeShape) == 13 * 4
+    assert C.sizeof(_lib.ShardDecodeShape) == 14 * 4
 
 
 def test_argument_validation_without_gpu():
@@ -60,7 +60,13 @@ def test_argument_validation_without_gpu():
     # sequence-split exchange: buffer = flags (2 slots x world x nkv u32, rounded to 256 B) + 2 slots of records
     assert lib.shard_b200_peer_buffer_bytes(2, 8) == 256 + 2 * 2 * 32 * 132 * 4
     assert lib.shard_b200_peer_buffer_bytes(17, 8) == 0
-    assert lib.shard_b200_seqsplit_merge(None, None, 0, 2, 8, 1, None, None, None) == -1
+    assert lib.shard_b200_seqsplit_merge(None, None, 0, 2, 8, 1, None, None, 0, None) == -1
+    assert lib.shard_b200_seqsplit_wait_merge(None, 0, 2, 8, 1, None, None, 0, None) == -1
+    sh1 = ops.make_shape(32, 8, 192, 1000, 0, 1000, 4, 64, 0, 1068, partial_out=False)
+    bufs = (C.c_void_p * 2)(1, 1)
+    assert lib.shard_b200_decode_attn_seqsplit(C.addressof(seq), C.byref(sh1), None, None, None, 0, bufs, 0, 2, 1,
+                                               None) == -1       # the record that travels is the partial one
+    assert lib.shard_b200_decode_status(None, None, None) == -1
     assert lib.shard_b200_vq_assign_accumulate(None, None, 10, None, None, None, None) == -1
     assert lib.shard_b200_phase_table_bytes(33) == 64 * 256
 
@@ -81,13 +87,66 @@ def test_split_ranges_cover_and_align():
             assert len(r) == w and r[0][0] == 0 and r[-1][1] == n
             for (a, b), (c, d) in zip(r[:-1], r[1:]):
                 assert b == c and a <= b
-            assert all(a % 16 == 0 for a, _ in r if a < n)
+            assert all(a % 128 == 0 for a, _ in r if a < n)
             sizes = [b - a for a, b in r]
-            assert max(sizes) - min(sizes) <= 16 + 15
+            assert max(sizes) - min(sizes) <= 128 + 127
     for n in (1, 7, 64):
         for w in (1, 2, 4, 8):
             got = sum((batch_shard(n, r, w) for r in range(w)), [])
             assert got == list(range(n))
+
+
+def test_host_tables_match_reference_fixtures():
+    """The product's own host-side tables -- Lloyd-Max codebook, per-layer sign vectors, DP bit
+    allocation -- against the values the reference produced (the kernels take them as inputs)."""
+    import json
+    from shard_b200.rope import dp_bit_allocation
+    from shard_b200.streaming import lloyd_max_codebook, stream_signs
+    g = load_golden("codebook.npz")
+    cb = lloyd_max_codebook(128, 8)
+    assert cb.dtype == torch.float32 and np.array_equal(cb.numpy(), g["codebook"])
+    for li in range(4):
+        assert np.array_equal(stream_signs(li, 128, "cpu").numpy(), g["signs"][li])
+    with open(os.path.join(REPO, "tests", "golden", "dp_alloc.json")) as f:
+        cases = json.load(f)
+    assert len(cases) >= 3
+    for c in cases:
+        assert list(dp_bit_allocation(torch.tensor(c["eig"], dtype=torch.float32), c["budget"])) == c["alloc"]
+
+
+def test_wrappers_refuse_tensors_of_another_device():
+    """Launches go to the current device's stream with raw pointers: a tensor of another GPU is
+    refused on the host (checked here with a stand-in tensor; no GPU needed)."""
+    from shard_b200 import _lib
+
+    class Dev:
+        index = 1
+
+    class T:
+        is_cuda = True
+        device = Dev()
+
+    _lib.require_cuda(T(), None, current=1)
+    with pytest.raises(_lib.ShardError, match="current device"):
+        _lib.require_cuda(T(), current=0)
+
+
+def test_empty_rank_contributes_neutral_record():
+    """Fewer tiles than ranks: the idle ranks' record (max = -inf, sum-exp = 0) gets weight zero."""
+    from shard_b200.parallel import neutral_partial, split_ranges
+    r = split_ranges(200, 4)
+    assert r == [(0, 128), (128, 200), (200, 200), (200, 200)]
+    rng = np.random.default_rng(0)
+    real = np.zeros((2, 32, 132), np.float32)
+    real[:, :, 0] = rng.standard_normal((2, 32))
+    real[:, :, 1] = 1 + rng.random((2, 32))
+    real[:, :, 4:] = rng.standard_normal((2, 32, 128))
+    idle = neutral_partial(32, "cpu").numpy()
+    assert np.isneginf(idle[:, 0]).all() and not idle[:, 1:].any()
+    parts = np.concatenate([real, idle[None], idle[None]])
+    a = O.lse_merge(real[:, :, 0], real[:, :, 1], real[:, :, 4:])
+    b = O.lse_merge(parts[:, :, 0], parts[:, :, 1], parts[:, :, 4:])
+    assert np.array_equal(a, b)
 
 
 def test_shard_layer_tokens_slices(golden_chain512):

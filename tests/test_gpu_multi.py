@@ -52,7 +52,34 @@ for step in range(5):
     torch.cuda.synchronize()
     peer.check()
     assert out2.cpu().numpy()[0, :, 0, :].tobytes() == got.tobytes(), step
+# fewer tiles than ranks: rank 1's range is empty, it launches no decode and contributes the neutral record
+tiny_np = random_gc(100, seed=8)
+tiny_full = FakeLayer(gc_to_device(tiny_np, f"cuda:{rank}"), FakeCache(inv))
+tiny_whole = decode_layer(q, tiny_full, 200).cpu().numpy()
+tiny_sub = shard_layer_tokens(tiny_full._gpu_compressed, rank, world)
+assert (tiny_sub["n_compress"] == 0) == (rank == 1)
+if tiny_sub["n_compress"]:
+    attach_kernel_format(tiny_sub, 8)
+tiny = FakeLayer(tiny_sub, FakeCache(inv))
+for p_ in (None, peer):
+    o = seqsplit_decode(q, tiny, 200, peer=p_).cpu().numpy()[0, :, 0, :]
+    assert np.abs(o.astype(np.float32) - tiny_whole.astype(np.float32)).max() <= 2e-3
+peer.check()
 peer.close()
+dist.barrier()
+# one process driving two GPUs: the kernel's shared-memory opt-in and the SM count are per device
+other = 1 - rank
+with torch.cuda.device(other):
+    layer_o = FakeLayer(gc_to_device(gc_np, f"cuda:{other}"), FakeCache(inv))
+    q_o = q.to(f"cuda:{other}")
+    got_o = decode_layer(q_o, layer_o, 5100).cpu().numpy()
+assert np.array_equal(got_o, ref)
+try:
+    decode_layer(q_o, full, 5100)            # tensors of two different devices in one call
+    raise SystemExit("a tensor of another device was accepted")
+except Exception as e:
+    assert "current device" in str(e), e
+dist.barrier()
 dist.destroy_process_group()
 print("ok", rank)
 '''

@@ -454,7 +454,7 @@ def test_batched_decoder_matches_single(ops, codebook):
 def test_cache_compress_and_decode_end_to_end(ops):
     """Prefill -> compress() -> streamed decode steps through the public classes."""
     from shard_b200 import Cache, fused_attention_compressed
-    from shard_b200 import synth
+    import synth
     k, v, q = synth.make_kvq(1024, 5)
     inv = synth.rope_inv_freq()
     cache = Cache(num_layers=1, rope_inv_freq=inv)
