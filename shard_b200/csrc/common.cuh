@@ -45,6 +45,7 @@ constexpr int PART = SHARD_PART_STRIDE;
 constexpr float SQRT_HD = 11.313708498984761f;
 constexpr float INV_SQRT_HD = 0.08838834764831845f;
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
 
 __device__ __forceinline__ float neg_inf() { return __int_as_float(0xff800000); }
 

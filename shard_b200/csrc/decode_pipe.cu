@@ -46,9 +46,11 @@ constexpr int PP_UNPACK_WARP0 = 12;
 constexpr int PP_WARPS = 16;
 constexpr int PP_THREADS = PP_WARPS * 32;
 constexpr int PP_TMEM_COLS = 512;
-constexpr int PP_COL_A = 384;         // A operand slot: R/2 coefficient columns + 8 constant columns (1, 0, ...)
-constexpr int PP_COL_S = 64;          // within a stage
-constexpr int PP_COL_O = 80;
+// tensor memory: two key stages of 128 columns, the A operand slot (R/2 coefficient columns + 8
+// constant columns 1, 0, ...), and per consumer group 16 columns of scores + 16 of P.V accumulator
+constexpr int PP_COL_A = 256;
+constexpr int PP_COL_SO = 360;
+constexpr float PP_LAZY_LOG2 = 8.f;   // a softmax reference point moves only when exceeded by more than 2^8
 constexpr int PP_V_BYTES = 32768, PP_P_BYTES = 4096, PP_Q_BYTES = 4096, PP_CB_BYTES = 2048;
 constexpr int PP_ROWQ_BYTES = (GQA * HD + 256) * 4;   // queries as given + stream codebook, for the row path
 constexpr int PP_MISC_BYTES = 1024 + 1024;   // state + barriers, and slack for 1 KB alignment
@@ -102,6 +104,8 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   constexpr int R = NW * 32;
   constexpr int KSTEPS = R / 16 + 1;   // + one step whose A columns are (1, 0, ...) and whose W slice is the mean
   constexpr int W_BYTES = pp_w_bytes(NW);
+  constexpr int W_ATOMS = W_BYTES / 16384;
+  constexpr int NSUB = (NW + 1) / 2;   // thirds of the A slot: 4 k-steps (64 ranks) each
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -121,7 +125,8 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(misc + 144);
   volatile int* abort_s = reinterpret_cast<volatile int*>(misc + 145);
   volatile int* c_cnt = reinterpret_cast<volatile int*>(misc + 146);   // [2] coefficient tiles requested per buffer
-  uint64_t* bars = reinterpret_cast<uint64_t*>(misc + 148);        // 25 mbarriers
+  volatile int* mma1_next = reinterpret_cast<volatile int*>(misc + 208);   // next tile whose MMA1 is to be issued
+  uint64_t* bars = reinterpret_cast<uint64_t*>(misc + 148);        // 28 mbarriers
 
   const ShardSeq& sq = p.table ? p.table[blockIdx.z] : p.one;
   const ShardDecodeShape& sh = p.sh;
@@ -162,16 +167,15 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
 
   // barrier addresses
   const uint32_t bar0 = smem_u32(bars);
-  auto KN_FULL = [&](int s) { return bar0 + 8u * (uint32_t)s; };          // MMA1 of the stage's tile done
-  auto S_FULL = [&](int s) { return bar0 + 8u * (uint32_t)(3 + s); };     // MMA2 done
-  auto O_FULL = [&](int s) { return bar0 + 8u * (uint32_t)(6 + s); };     // MMA3 done
-  auto T_EMPTY = [&](int s) { return bar0 + 8u * (uint32_t)(9 + s); };    // consumers have drained the stage
+  auto KN_FULL = [&](int g) { return bar0 + 8u * (uint32_t)g; };          // MMA1 of group g's next tile done
+  auto S_FULL = [&](int g) { return bar0 + 8u * (uint32_t)(3 + g); };     // MMA2 done
+  auto O_DONE = [&](int g) { return bar0 + 8u * (uint32_t)(6 + g); };     // MMA3 done (V tile, P and O of the group are free / final)
   auto A_EMPTY = [&](int j) { return bar0 + 8u * (uint32_t)(12 + j); };   // MMA1 has read third j of the A slot
-  auto A_FULL = [&](int g) { return bar0 + 8u * (uint32_t)(21 + g); };    // the A operand of group g's next tile is in place
+  auto A_FULL = [&](int j) { return bar0 + 8u * (uint32_t)(25 + j); };    // third j of the next tile's A operand is in place
+  auto W_FULL = [&](int a) { return bar0 + 8u * (uint32_t)(15 + a); };    // atom a (64 contraction positions) of the weights has landed
+  auto C_FULL = [&](int b) { return bar0 + 8u * (uint32_t)(19 + b); };    // coefficient tile has landed
+  auto V_FULL = [&](int g) { return bar0 + 8u * (uint32_t)(21 + g); };    // V code tile has landed
   const uint32_t APPEND_DONE = bar0 + 8u * 24u;                           // the newest streamed row has been written
-  const uint32_t W_FULL = bar0 + 8u * 15u;                                // weights have landed
-  auto C_FULL = [&](int b) { return bar0 + 8u * (uint32_t)(16 + b); };    // coefficient tile has landed
-  auto V_FULL = [&](int g) { return bar0 + 8u * (uint32_t)(18 + g); };    // V code tile has landed
 
   // tiles of this chunk: evenly spread, the first `tiles_rem` chunks get one more
   const int tile_lo = part * p.tiles_per_chunk + min(part, p.tiles_rem);
@@ -201,22 +205,27 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   }
   if (tid == 0) {
     // first the barriers of the bulk copies, so that the copy engine starts as early as possible:
-    // the weights, two coefficient tiles, and the first V code tile of every consumer group
-    mbar_init(C_FULL(0), 1); mbar_init(C_FULL(1), 1); mbar_init(W_FULL, 1);
+    // the first coefficient tile, the weights atom by atom (the first k-steps only need the first
+    // atom), the second coefficient tile and the first V code tile of every consumer group
+    mbar_init(C_FULL(0), 1); mbar_init(C_FULL(1), 1);
+    for (int a = 0; a < W_ATOMS; ++a) mbar_init(W_FULL(a), 1);
     for (int g = 0; g < PP_STAGES; ++g) mbar_init(V_FULL(g), 1);
     c_cnt[0] = n_my > 0 ? 1 : 0; c_cnt[1] = n_my > 1 ? 1 : 0;
     fence_mbar_init();
     if (n_my > 0) issue_coef(0);
-    mbar_expect_tx(W_FULL, (uint32_t)W_BYTES);
-    bulk_g2s(smem_u32(w_s), reinterpret_cast<const unsigned char*>(sq.k_wprep) + (size_t)kv * W_BYTES,
-             (uint32_t)W_BYTES, W_FULL);
+    for (int a = 0; a < W_ATOMS; ++a) {
+      mbar_expect_tx(W_FULL(a), 16384u);
+      bulk_g2s(smem_u32(w_s + a * 16384), reinterpret_cast<const unsigned char*>(sq.k_wprep) + (size_t)kv * W_BYTES + a * 16384,
+               16384u, W_FULL(a));
+    }
     if (n_my > 1) issue_coef(1);
     for (int j = 0; j < min(PP_STAGES, n_my); ++j) issue_vcodes(j);
   } else if (tid == 32) {
     for (int s = 0; s < PP_STAGES; ++s) {
-      mbar_init(KN_FULL(s), 1); mbar_init(S_FULL(s), 1); mbar_init(O_FULL(s), 1); mbar_init(T_EMPTY(s), 4);
-      mbar_init(A_EMPTY(s), 1); mbar_init(A_FULL(s), 4);
+      mbar_init(KN_FULL(s), 1); mbar_init(S_FULL(s), 1); mbar_init(O_DONE(s), 1); mbar_init(A_EMPTY(s), 1);
     }
+    *mma1_next = 0;
+    for (int j = 0; j < 3; ++j) mbar_init(A_FULL(j), 4);
     mbar_init(APPEND_DONE, 2);
     *abort_s = 0;
     fence_mbar_init();
@@ -273,11 +282,11 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   if (warp < PP_CONS_WARPS) {
     // =============================== consumer groups ======================================
     const int g = warp >> 2, quad = warp & 3, m = quad * 32 + lane;
-    // the four MMA-issuing threads of the CTA (one per consumer group + one unpack warp) sit on
-    // four different warp schedulers: group g issues from its warp g + 1, the unpack side from warp 12
+    // the MMA-issuing threads of the CTA (one per consumer group + the unpack side's) sit on four
+    // different warp schedulers: group g issues from its warp g + 1, the unpack side from warp 12
     const int issuer_quad = g + 1;
-    const uint32_t T_g = tmem_base + (uint32_t)(128 * g);
-    const uint32_t lane_T = T_g + ((uint32_t)(quad * 32) << 16);
+    const uint32_t SO_g = tmem_base + (uint32_t)(PP_COL_SO + 32 * g);      // scores at +0, P.V accumulator at +16
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     constexpr uint32_t IDESC2 = umma_idesc(128, 16, false, false);
     constexpr uint32_t IDESC3 = umma_idesc(128, 16, true, false);
     const uint64_t qdesc = smem_desc_sw128(smem_u32(q_s), 16, 1024);
@@ -287,35 +296,55 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     unsigned char* p_g = p_s + g * PP_P_BYTES;
     float* alpha_g = alpha_s + 16 * g;
     const uint4* phase_tab = reinterpret_cast<const uint4*>(sq.phase);
-    const uint4* vc_row = reinterpret_cast<const uint4*>(vc_s + g * PP_VC_BYTES + m * VQ_GROUPS);
+    const unsigned char* vc_g = vc_s + g * PP_VC_BYTES;
     int vc_issued = g < n_my ? 1 : 0;        // V code tiles requested for this group so far
     const bool issuer = quad == issuer_quad && lane == 0;
-    // MMA1 of tile `it` (one of this group's tiles), issued by the group's issuing thread as soon as
-    // the unpack warps have the A operand in place and the group has drained its stage.  The A slot
-    // is handed back to the unpack warps third by third while the later k-steps still run.
+    // MMA1 of tile t: K_n[128 tok x 128] = A . W^T into key stage t % 2, issued third by third of the A
+    // slot as the unpack warps fill it, each third handed back as soon as its k-steps have run.
+    // Issued by a consumer group's issuing thread: tiles 0 and 1 at the start, tile t >= 2 by the
+    // thread that has just issued the scores product of tile t - 2 out of the same key stage (one
+    // thread's tensor-core instructions run in issue order, so the stage is not overwritten early).
+    // `mma1_next` keeps the issuing threads in tile order.  A k-step of 128 columns holds its
+    // issuing thread for about as long as the previous one runs (about 900 cycles per tile), which
+    // is why the issuing thread's warp takes no part in expanding the V codes: its three sibling
+    // warps do that for all 128 tokens meanwhile.
     constexpr uint32_t IDESC1 = umma_idesc(128, 128, false, false);
-    constexpr int NSUB = (NW + 1) / 2;       // thirds of the A slot: 4 k-steps (64 ranks) each
     const uint64_t wdesc = smem_desc_sw128(smem_u32(w_s), 16, 1024);
-    auto issue_mma1 = [&](int it) -> bool {
-      const int use = it / PP_STAGES;
-      if (!mbar_wait(A_FULL(g), (uint32_t)(use & 1), abort_s)) return false;
-      if (it + 2 < n_my) { issue_coef(it + 2); c_cnt[it & 1] = c_cnt[it & 1] + 1; }   // the unpack warps are done with that buffer
-      if (it == 0 && !mbar_wait(W_FULL, 0u, abort_s)) return false;
-      if (use > 0 && !mbar_wait(T_EMPTY(g), (uint32_t)((use - 1) & 1), abort_s)) return false;
-      tc_fence_after();
-#pragma unroll
-      for (int ks = 0; ks < KSTEPS; ++ks) {
-        umma_ts_1t(T_g, tmem_base + PP_COL_A + 8 * ks, wdesc + (uint64_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4),
-                   IDESC1, ks > 0 ? 1u : 0u);
-        if ((ks & 3) == 3 && ks / 4 < NSUB - 1) umma_commit_1t(A_EMPTY(ks / 4));
+    auto issue_mma1 = [&](int t) -> bool {
+      int spins = 0;
+      while (*mma1_next != t) {
+        if (++spins > (1 << 20) || *abort_s) { *abort_s = 1; return false; }
+        __nanosleep(32);
       }
-      umma_commit_1t(A_EMPTY(NSUB - 1));
-      umma_commit_1t(KN_FULL(g));
+      const uint32_t T_t = tmem_base + (uint32_t)(128 * (t & 1));
+#pragma unroll
+      for (int j = 0; j < NSUB; ++j) {
+        if (!mbar_wait(A_FULL(j), (uint32_t)(t & 1), abort_s)) return false;
+        if (t == 0) {                                             // only the very first MMA1 can be ahead of the weights
+          if (!mbar_wait(W_FULL(j), 0u, abort_s)) return false;
+          if (j == NSUB - 1 && W_ATOMS > NSUB && !mbar_wait(W_FULL(W_ATOMS - 1), 0u, abort_s)) return false;
+        }
+        tc_fence_after();
+        const int ks_hi = (j == NSUB - 1) ? KSTEPS : 4 * j + 4;
+#pragma unroll
+        for (int ks = 4 * j; ks < 4 * j + 5; ++ks) {
+          if (ks < ks_hi)
+            umma_ts_1t(T_t, tmem_base + PP_COL_A + 8 * ks, wdesc + (uint64_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4),
+                       IDESC1, ks > 0 ? 1u : 0u);
+        }
+        umma_commit_1t(A_EMPTY(j));
+      }
+      umma_commit_1t(KN_FULL(t % PP_STAGES));
+      if (t + 2 < n_my) { issue_coef(t + 2); c_cnt[t & 1] = c_cnt[t & 1] + 1; }   // the unpack warps are done with that buffer
+      *mma1_next = t + 1;
       return true;
     };
+    // gather work of the three non-issuing warps: 512 units of (token row, 8 codes), 96 threads
+    const int gq = quad - (quad > issuer_quad ? 1 : 0);        // 0..2 among the gathering warps
+    const int gather_first = gq * 32 + lane;
 
     bool bad = false;
-    if (issuer && g < n_my) bad |= !issue_mma1(g);
+    if (issuer && g < 2 && g < n_my) bad |= !issue_mma1(g);
     __syncwarp();
     // Fused append: in the CTA that owns the newest streamed row, two warps of the last consumer
     // group -- whose first tile is the furthest away -- quantise the new token now.  The row is
@@ -325,8 +354,11 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       __syncwarp();
       if (lane == 0) mbar_arrive(APPEND_DONE);
     }
-    for (int it = g; it < n_my; it += PP_STAGES) {
-      const uint32_t par = (uint32_t)((it / PP_STAGES) & 1);
+    int use = 0;
+    for (int it = g; it < n_my; it += PP_STAGES, ++use) {
+      const uint32_t par = (uint32_t)(use & 1);
+      const uint32_t T_s = tmem_base + (uint32_t)(128 * (it & 1));   // key stage of this tile
+      const uint32_t lane_T = T_s + lane_off;
       const int t0 = sh.tok_begin + (tile_lo + it) * 128;
       const int tok = min(t0 + m, sh.tok_end - 1);
       const bool valid = (t0 + m) < sh.tok_end;
@@ -338,6 +370,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       pc[0] = prow[0 * 32]; ps[0] = prow[8 * 32];
       pc[1] = prow[1 * 32]; ps[1] = prow[9 * 32];
       pc[2] = prow[2 * 32]; ps[2] = prow[10 * 32];
+
       bad |= !mbar_wait(KN_FULL(g), par, abort_s);
       tc_fence_after();
 
@@ -369,44 +402,56 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       tc_fence_before();
       bad = named_bar_or(1 + g, 128, bad || *abort_s);
       if (bad) break;                                   // uniform over the group
-      if (quad == issuer_quad && lane == 0) {
+      if (issuer) {
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_ts_1t(T_g + PP_COL_S, T_g + 8 * ks, qdesc + (uint64_t)(((ks >> 2) * 2048 + (ks & 3) * 32) >> 4), IDESC2,
+          umma_ts_1t(SO_g, T_s + 8 * ks, qdesc + (uint64_t)(((ks >> 2) * 2048 + (ks & 3) * 32) >> 4), IDESC2,
                      ks > 0 ? 1u : 0u);
         umma_commit_1t(S_FULL(g));
+        if (it + 2 < n_my) bad |= !issue_mma1(it + 2);  // the same key stage, behind the scores product
       }
       __syncwarp();
       // (while the tensor core computes the scores)
-      // ---- gather the token's V row (32 codes) into the stage's V tile -------------------------
+      // ---- gather the token's V row (32 codes) into the group's V tile ---------------------------
+      // the previous tile's P.V product must have finished reading the V tile and P
+      if (use > 0) bad |= !mbar_wait(O_DONE(g), (uint32_t)((use - 1) & 1), abort_s);
       bad |= !mbar_wait(V_FULL(g), par, abort_s);
-      {
-        const uint4 codes0 = vc_row[0], codes1 = vc_row[1];
-        const uint32_t cw[8] = {codes0.x, codes0.y, codes0.z, codes0.w, codes1.x, codes1.y, codes1.z, codes1.w};
+      if (quad != issuer_quad) {
+#pragma unroll 2
+        for (int u = gather_first; u < 512; u += 96) {
+          const int row = u >> 2, part = u & 3;               // codes 8*part .. 8*part+7 of the row
+          const uint2 cw = *reinterpret_cast<const uint2*>(vc_g + row * VQ_GROUPS + 8 * part);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const uint32_t two = cw[j >> 1] >> (16 * (j & 1));
-          const uint2 e0 = cbv[two & 0xff], e1 = cbv[(two >> 8) & 0xff];
-          *reinterpret_cast<uint4*>(v_g + (j >> 3) * 16384 + sw128_off(m, j & 7)) = make_uint4(e0.x, e0.y, e1.x, e1.y);
+          for (int jj = 0; jj < 4; ++jj) {
+            const uint32_t two = (jj < 2 ? cw.x : cw.y) >> (16 * (jj & 1));
+            const uint2 e0 = cbv[two & 0xff], e1 = cbv[(two >> 8) & 0xff];
+            const int j = 4 * part + jj;                      // 8-channel chunk of the row
+            *reinterpret_cast<uint4*>(v_g + (j >> 3) * 16384 + sw128_off(row, j & 7)) = make_uint4(e0.x, e0.y, e1.x, e1.y);
+          }
         }
       }
 
       // ---- softmax over this warp's 32 tokens ---------------------------------------------------
+      // The reference point of a (warp, head) only moves when the tile's maximum exceeds it by more
+      // than 2^PP_LAZY_LOG2 (weights then stay below that factor, far inside fp16 range): the
+      // accumulator in tensor memory is rescaled only in those rare tiles.
       bad |= !mbar_wait(S_FULL(g), par, abort_s);
       tc_fence_after();
       {
         uint32_t sraw[4];
-        tmem_ld_x4(lane_T + PP_COL_S, sraw);
+        tmem_ld_x4(SO_g + lane_off, sraw);
         tmem_wait_ld();
 #pragma unroll
         for (int h = 0; h < GQA; ++h) {
-          const float s = valid ? __uint_as_float(sraw[h]) * INV_SQRT_HD : neg_inf();
-          const float tm = warp_max(s);
-          const float mn = fmaxf(run_m[h], tm);
-          const float al = (run_m[h] == neg_inf()) ? 0.f : exp2f((run_m[h] - mn) * LOG2E);
-          const float pr = valid ? exp2f((s - mn) * LOG2E) : 0.f;
-          run_m[h] = mn;
+          const float s2 = valid ? __uint_as_float(sraw[h]) * (INV_SQRT_HD * LOG2E) : neg_inf();   // log2 domain
+          const float tm = warp_max(s2);
+          float al = 1.f;
+          if (tm > run_m[h] + PP_LAZY_LOG2) {            // also the first tile with a valid token (run_m = -inf)
+            al = (run_m[h] == neg_inf()) ? 0.f : exp2f(run_m[h] - tm);
+            run_m[h] = tm;
+          }
+          const float pr = valid ? exp2f(s2 - run_m[h]) : 0.f;
           run_l[h] = run_l[h] * al + pr;
           const int n = 4 * quad + h;
           *reinterpret_cast<__half*>(p_g + (m >> 6) * 2048 + sw128_off(n, (m >> 3) & 7) + (m & 7) * 2) = __float2half_rn(pr);
@@ -417,45 +462,58 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       tc_fence_before();
       bad = named_bar_or(1 + g, 128, bad || *abort_s);
       if (bad) break;                                   // uniform over the group
-      if (quad == issuer_quad && lane == 0) {
+      if (use > 0) {
+        // rescale channel m of the accumulator where a reference point moved (same decision in
+        // every thread of the group: all read the same 16 factors)
+        float al[16];
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+          const float4 a4 = *reinterpret_cast<const float4*>(alpha_g + 4 * j4);
+          al[4 * j4] = a4.x; al[4 * j4 + 1] = a4.y; al[4 * j4 + 2] = a4.z; al[4 * j4 + 3] = a4.w;
+        }
+        bool moved = false;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) moved |= al[j] != 1.f;
+        if (moved) {
+          uint32_t o[16];
+          tmem_ld_x16(SO_g + 16 + lane_off, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * al[j]);
+          tmem_st_x16(SO_g + 16 + lane_off, o);
+          tmem_wait_st();
+          tc_fence_before();
+          named_bar_sync(1 + g, 128);
+        }
+      }
+      if (issuer) {
         if (it + PP_STAGES < n_my) { issue_vcodes(it + PP_STAGES); ++vc_issued; }   // every lane has read its codes
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          umma_ss_1t(T_g + PP_COL_O, vdesc + (uint64_t)((ks * 2048) >> 4),
-                     pdesc + (uint64_t)(((ks >> 2) * 2048 + (ks & 3) * 32) >> 4), IDESC3, ks > 0 ? 1u : 0u);
-        umma_commit_1t(O_FULL(g));
+          umma_ss_1t(SO_g + 16, vdesc + (uint64_t)((ks * 2048) >> 4),
+                     pdesc + (uint64_t)(((ks >> 2) * 2048 + (ks & 3) * 32) >> 4), IDESC3, (ks > 0 || use > 0) ? 1u : 0u);
+        umma_commit_1t(O_DONE(g));
       }
       __syncwarp();
-
-      // ---- accumulate channel m of the tile's P.V ------------------------------------------------
-      bad |= !mbar_wait(O_FULL(g), par, abort_s);
+    }
+    // the group's accumulated P.V: channel m, 16 (warp, head) columns
+    if (use > 0 && !(bad || *abort_s)) {
+      bad |= !mbar_wait(O_DONE(g), (uint32_t)((use - 1) & 1), abort_s);
       tc_fence_after();
-      {
+      if (!bad) {
         uint32_t o[16];
-        tmem_ld_x16(lane_T + PP_COL_O, o);
+        tmem_ld_x16(SO_g + 16 + lane_off, o);
         tmem_wait_ld();
 #pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          const float4 al = *reinterpret_cast<const float4*>(alpha_g + 4 * j4);
-          acc[4 * j4 + 0] = fmaf(acc[4 * j4 + 0], al.x, __uint_as_float(o[4 * j4 + 0]));
-          acc[4 * j4 + 1] = fmaf(acc[4 * j4 + 1], al.y, __uint_as_float(o[4 * j4 + 1]));
-          acc[4 * j4 + 2] = fmaf(acc[4 * j4 + 2], al.z, __uint_as_float(o[4 * j4 + 2]));
-          acc[4 * j4 + 3] = fmaf(acc[4 * j4 + 3], al.w, __uint_as_float(o[4 * j4 + 3]));
-        }
+        for (int j = 0; j < 16; ++j) acc[j] = __uint_as_float(o[j]);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(T_EMPTY(g));
-      if (issuer && it + PP_STAGES < n_my) bad |= !issue_mma1(it + PP_STAGES);
-      __syncwarp();
     }
     // giving up: do not leave while a copy this thread asked for may still be landing
     if ((bad || *abort_s) && issuer && vc_issued > 0)
       mbar_wait(V_FULL(g), (uint32_t)((vc_issued - 1) & 1), abort_s);
   } else {
     // =============================== unpack warps =========================================
-    constexpr int NSUB = (NW + 1) / 2;
     const int quad = warp - PP_UNPACK_WARP0, m = quad * 32 + lane;
     const uint32_t lane_A = tmem_base + PP_COL_A + ((uint32_t)(quad * 32) << 16);
     {
@@ -489,12 +547,11 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
           }
           tmem_st_x16(lane_A + 16 * i, o);
         }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(A_FULL(j));          // this warp's rows of the third are in place
       }
-      if (bad) break;
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(A_FULL(it % PP_STAGES));   // this warp's rows are in place, its reads of c_s done
     }
     // The unpack warps run about three tiles ahead of the consumers.  In that slack they take this
     // CTA's share of the fp16 / streamed rows (row u belongs to CTA u % n_row_parts), one warp per
@@ -530,6 +587,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   }
   __syncthreads();
   {
+    // run_m is kept in the log2 domain (score * log2 e); the record carries the natural-log maximum
     const int h = tid >> 7, m = tid & 127;              // 512 threads: one (head, channel) each
     float M = neg_inf();
 #pragma unroll
@@ -539,17 +597,17 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     for (int e = 0; e < 12; ++e) {
       const int idx = 16 * (e >> 2) + 4 * (e & 3) + h;
       const float mv = m_s[idx];
-      const float wt = (mv == neg_inf()) ? 0.f : exp2f((mv - M) * LOG2E);
+      const float wt = (mv == neg_inf()) ? 0.f : exp2f(mv - M);
       L = fmaf(wt, l_s[idx], L);
       a = fmaf(wt, reinterpret_cast<const float*>(v_s + (e >> 2) * PP_V_BYTES)[(4 * (e & 3) + h) * HD + m], a);
     }
     float* rec = rec_base + h * PART;
-    if (m == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
+    if (m == 0) { rec[0] = M * LN2; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
     rec[4 + m] = a * ch_scale;
   }
   if (tid == 0 && *abort_s) {
     // gave up somewhere: do not leave while a bulk copy may still be landing in this CTA's memory
-    mbar_wait(W_FULL, 0u, abort_s);
+    for (int a = 0; a < W_ATOMS; ++a) mbar_wait(W_FULL(a), 0u, abort_s);
     for (int b = 0; b < 2; ++b)
       if (c_cnt[b] > 0) mbar_wait(C_FULL(b), (uint32_t)((c_cnt[b] - 1) & 1), abort_s);
     if (p.status) atomicExch(p.status, 1);
