@@ -531,14 +531,14 @@ def measure_seqsplit(D, L, K, W, T=131072, merge="peer", with_n1=True):
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K * L)]
     peer = PeerExchange(N_KV) if (D.world > 1 and merge in ("peer", "both")) else None
 
-    def step(j, timed, use_peer):
+    def step(j, events, use_peer):
         pos = T + j
         cache._fused_decode_update = True
         for li in range(L):
             layer = cache.layers[li]
             if first:
                 layer.update(k_pool[j, li], v_pool[j, li])           # stream append (rank 0 owns the stream)
-            e = ev[(j - W) * L + li] if timed else None
+            e = ev[(j - W) * L + li] if events else None
             if e: e[0].record()
             if use_peer:
                 decode_layer(q_pool[j, li], layer, pos, partial_out=True, with_fp16_segments=first, push=peer)
@@ -555,7 +555,11 @@ def measure_seqsplit(D, L, K, W, T=131072, merge="peer", with_n1=True):
             if e: e[2].record()
         cache._fused_decode_update = False
 
-    def timed_run(use_peer, steps):
+    def timed_run(use_peer, steps, events):
+        """ms per step (max over ranks) of `steps` decode steps; with `events` also the decode / merge
+        split per step from CUDA events around every launch (an event record between two launches
+        keeps the second from starting early behind the first, so the split is taken in a pass of
+        its own and the headline number in a pass without events)."""
         for j in range(W):
             step(j, False, use_peer)
         D.barrier()
@@ -563,26 +567,34 @@ def measure_seqsplit(D, L, K, W, T=131072, merge="peer", with_n1=True):
         D.barrier()
         ev0.record()
         for j in range(W, W + steps):
-            step(j, True, use_peer)
+            step(j, events, use_peer)
         ev1.record()
         D.barrier()
         ms_total = ev0.elapsed_time(ev1)
-        used = ev[: steps * L]
-        dec_ms = sum(e[0].elapsed_time(e[1]) for e in used) / steps
-        mrg_ms = sum(e[1].elapsed_time(e[2]) for e in used) / steps
+        dec_ms = mrg_ms = 0.0
+        if events:
+            used = ev[: steps * L]
+            dec_ms = sum(e[0].elapsed_time(e[1]) for e in used) / steps
+            mrg_ms = sum(e[1].elapsed_time(e[2]) for e in used) / steps
         return D.max_over_ranks([ms_total / steps, dec_ms, mrg_ms])
 
     res = {"workload": f"cfg4: one {T}-token sequence, {L} layers, compressed middle split into {D.world} contiguous "
                        "token range(s) (random codes); rank 0 also owns sink, window and stream", "steps": K}
-    ms_step, dec_ms, mrg_ms = timed_run(peer is not None, K)
-    res.update(us_per_layer=ms_step * 1e3 / L, decode_us_per_layer=dec_ms * 1e3 / L,
-               merge_us_per_layer=mrg_ms * 1e3 / L,
+    kb = min(K, 8)
+    ms_step, _, _ = timed_run(peer is not None, K, False)
+    ms_b, dec_ms, mrg_ms = timed_run(peer is not None, kb, True)
+    res.update(us_per_layer=ms_step * 1e3 / L,
+               breakdown={"steps": kb, "us_per_layer": ms_b * 1e3 / L, "decode_us_per_layer": dec_ms * 1e3 / L,
+                          "merge_us_per_layer": mrg_ms * 1e3 / L,
+                          "note": "pass with CUDA events around every launch (no launch overlap)"},
+               decode_us_per_layer=dec_ms * 1e3 / L, merge_us_per_layer=mrg_ms * 1e3 / L,
                merge="decode launch delivers over NVLink peer memory + polling merge kernel" if peer is not None
                else ("NCCL all-gather + merge launch" if D.world > 1 else "single GPU: merge launch only"))
     if D.world > 1 and merge == "both":
         # the NCCL path beside it (the stream keeps growing meanwhile: well under 1 us per layer on rank 0)
         k2 = min(K, 16)
-        ms2, dec2, mrg2 = timed_run(False, k2)
+        ms2, _, _ = timed_run(False, k2, False)
+        _, dec2, mrg2 = timed_run(False, kb, True)
         res["nccl"] = {"us_per_layer": ms2 * 1e3 / L, "decode_us_per_layer": dec2 * 1e3 / L,
                        "merge_us_per_layer": mrg2 * 1e3 / L, "steps": k2}
     n_local = end - begin

@@ -70,7 +70,7 @@ typedef struct ShardSeq {
   void* out;                 /* fp16 [n_q][128] result, or fp32 [n_q][132] partial      */
   const void* new_k;         /* fp16 [nkv][128]   token to append (stream_quantize)     */
   const void* new_v;         /* fp16 [nkv][128]                                         */
-  const void* dec_k;         /* fp16 [nkv][n_dec][128] tokens appended as they are by a */
+  const void* dec_k;         /* fp16 [nkv][dec_cap or n_dec][128] tokens appended as they are by a */
   const void* dec_v;         /* non-streaming cache (gc["decode_k"], gc["decode_v"])    */
 } ShardSeq;
 
@@ -90,6 +90,7 @@ typedef struct ShardDecodeShape {
   int32_t append;         /* 1: first quantise new_k/new_v into stream row n_stream-1 (fused append) */
   int32_t n_dec;          /* rows of the fp16 decode buffer (dec_k / dec_v)              */
   int32_t no_overlap;     /* 1: plain launch, no early start behind the preceding kernel (see decode_attn) */
+  int32_t dec_cap;        /* rows allocated per KV head in dec_k / dec_v (0: exactly n_dec)    */
 } ShardDecodeShape;
 
 /*

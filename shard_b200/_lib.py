@@ -29,7 +29,7 @@ class ShardDecodeShape(C.Structure):
     """Mirror of `struct ShardDecodeShape`."""
     _fields_ = [(name, C.c_int32) for name in (
         "n_q", "nkv", "rank", "n_comp", "tok_begin", "tok_end",
-        "n_sink", "n_win", "n_stream", "pos_q", "partial_out", "append", "n_dec", "no_overlap")]
+        "n_sink", "n_win", "n_stream", "pos_q", "partial_out", "append", "n_dec", "no_overlap", "dec_cap")]
 
 
 _SIGNATURES = {

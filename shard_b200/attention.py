@@ -56,20 +56,25 @@ def _seq_record(gc, dev):
 
 class _Launch:
     """Per-layer launch state that does not change from step to step: the sequence record, the
-    shape record (only n_stream / pos_q / append are touched per step), workspace need and
-    the constant device pointers."""
-    __slots__ = ("key", "seq", "shape", "need", "inv_ptr", "cb", "cb_ptr")
+    shape record (only n_stream / pos_q / append / n_dec are touched per step), workspace need
+    and the constant device pointers."""
+    __slots__ = ("key", "seq", "shape", "need", "inv_ptr", "cb", "cb_ptr", "dev", "dev_index", "kbuf")
 
 
 def _launch_state(gc, cache, dev, nkv, n_q, t0, t1, with_fp16_segments, partial_out):
     n_sink = gc["sink_k"].shape[2] if with_fp16_segments else 0
     n_win = gc["win_k"].shape[2] if with_fp16_segments else 0
-    key = (t0, t1, n_sink, n_win, bool(partial_out), gc["n_compress"], gc["k_rank_kernel"], str(dev))
+    key = (t0, t1, n_sink, n_win, bool(partial_out), gc["n_compress"], gc["k_rank_kernel"], dev)
     ls = gc.get("_launch")
     if ls is None or ls.key != key:
+        _lib.require_cuda(gc["k_wprep"], gc["v_indices_u8"])       # same device as the query, and the current one
+        if gc["k_wprep"].device != dev:
+            raise _lib.ShardError(f"query on {dev} but the cache lives on {gc['k_wprep'].device}")
         ls = _Launch()
         ls.key = key
+        ls.dev, ls.dev_index = dev, dev.index
         ls.seq = _seq_record(gc, dev)
+        ls.kbuf = None
         ls.shape = ops.make_shape(n_q, nkv, gc["k_rank_kernel"], gc["n_compress"], t0, t1, n_sink, n_win, 0, 0,
                                   partial_out)
         # With a middle segment the scratch size does not depend on the number of rows (they ride
@@ -102,7 +107,8 @@ def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_f
     """
     gc = layer._gpu_compressed
     cache = layer._cache_ref
-    _lib.require_cuda(q_rope, gc["k_wprep"])
+    if not q_rope.is_cuda:
+        raise _lib.ShardError("shard_b200 kernels need CUDA tensors; there is no CPU fallback")
     B, n_q, s_q, hd = q_rope.shape
     nkv = cache._n_kv_heads
     if B != 1 or s_q != 1:
@@ -114,6 +120,11 @@ def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_f
     dev = q_rope.device
     t0, t1 = (0, gc["n_compress"]) if tok_range is None else tok_range
     ls = _launch_state(gc, cache, dev, nkv, n_q, t0, t1, with_fp16_segments, partial_out)
+    # kernels go to the current device's current stream with raw pointers: the tensors must live there
+    cur = torch.cuda.current_device()
+    if cur != ls.dev_index:
+        raise _lib.ShardError(f"tensor lives on cuda:{ls.dev_index} but the current device is cuda:{cur}; "
+                              "make the tensor's device current (torch.cuda.device) before the call")
     n_stream = gc.get("stream_n", 0) if with_fp16_segments else 0
     pending = gc.pop("_pending", None)
     if pending is not None and (not with_fp16_segments or pending[2] != n_stream - 1):
@@ -123,28 +134,28 @@ def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_f
     seq, shape = ls.seq, ls.shape
     if n_stream > 0:
         kbuf = gc["k_idx_buf"]
-        if seq.st_k_idx != kbuf.data_ptr():            # the stream buffers were (re)allocated
+        if ls.kbuf is not kbuf:                        # the stream buffers were (re)allocated
+            ls.kbuf = kbuf
             seq.st_k_idx, seq.st_v_idx = kbuf.data_ptr(), gc["v_idx_buf"].data_ptr()
             seq.st_k_norm, seq.st_v_norm = gc["k_norm_buf"].data_ptr(), gc["v_norm_buf"].data_ptr()
             seq.signs = gc["signs"].data_ptr()
     if pending is not None:
         seq.new_k, seq.new_v = pending[0].data_ptr(), pending[1].data_ptr()
-    n_dec = 0
+    n_dec = dec_cap = 0
     if with_fp16_segments and "decode_k" in gc:
-        # tokens a non-streaming cache appends as they are: (1, nkv, s, 128) fp16, re-made by torch.cat
-        # on every step, so the pointers are refreshed on every call
+        # tokens a non-streaming cache appends as they are: views of the rows in use of buffers
+        # (1, nkv, capacity, 128) allocated ahead, or plain (1, nkv, s, 128) tensors
         dk, dv = gc["decode_k"], gc["decode_v"]
         if dk.dtype != torch.float16:
             raise NotImplementedError("fp16 models only")
-        if not dk.is_contiguous():
-            dk = gc["decode_k"] = dk.contiguous()
-        if not dv.is_contiguous():
-            dv = gc["decode_v"] = dv.contiguous()
+        if dk.stride(3) != 1 or dk.stride(2) != hd or dv.stride(3) != 1 or dv.stride(2) != hd or dv.stride(1) != dk.stride(1):
+            dk, dv = gc["decode_k"], gc["decode_v"] = dk.contiguous(), dv.contiguous()
         n_dec = dk.shape[2]
+        dec_cap = dk.stride(1) // hd if nkv > 1 else n_dec   # rows allocated per KV head
         seq.dec_k, seq.dec_v = dk.data_ptr(), dv.data_ptr()
-    q2 = q_rope.reshape(n_q, hd)
-    if not q2.is_contiguous():
-        q2 = q2.contiguous()
+    q2 = q_rope
+    if q2.stride(3) != 1 or q2.stride(1) != hd:
+        q2 = q_rope.reshape(n_q, hd).contiguous()
     if push is not None and not partial_out:
         raise _lib.ShardError("a launch that delivers to the peers emits the partial record")
     if out is None and push is None:
@@ -156,7 +167,7 @@ def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_f
     seq.q, seq.out = q2.data_ptr(), (None if out is None else out.data_ptr())
     seq.phase = _phase_for(cache, gc, pos_q, t0, t1, dev).data_ptr() if t1 > t0 else None
     shape.n_stream, shape.pos_q, shape.append = n_stream, int(pos_q), int(pending is not None)
-    shape.n_dec = n_dec
+    shape.n_dec, shape.dec_cap = n_dec, dec_cap
     # the first launch on a freshly built dictionary follows the kernels that wrote its codes and
     # weights: it must not start early behind them
     shape.no_overlap = int(gc.pop("_fresh", False))

@@ -186,10 +186,27 @@ class CacheLayer(CacheLayerMixin):
         if self.layer_idx == 0 and c is not None and not c._compressed:
             c.compress()
 
-        self._lazy_evict()
         gc = self._gpu_compressed
         fused = bool(getattr(c, "_fused_decode_update", False))
+        if fused and gc is not None and seq_new == 1 and c._streaming:
+            # the decode hot path: the token is handed to the next decode launch, which quantises it
+            # into its stream row; nothing is launched here
+            if "_pending" in gc:
+                self._flush_pending()
+            s = gc.get("stream_n", 0)
+            if "signs" not in gc or s >= gc["k_idx_buf"].shape[0]:
+                self._grow_stream(gc, key_states, s + 1)
+            k2, v2 = key_states, value_states
+            if k2.stride(3) != 1 or k2.stride(1) != k2.shape[3] or v2.stride(3) != 1 or v2.stride(1) != v2.shape[3]:
+                k2, v2 = k2.contiguous(), v2.contiguous()
+            gc["_pending"] = (k2, v2, s)
+            gc["stream_n"] = s + 1
+            self._seq_len += 1
+            self._needs_decompress = True
+            c._last_accessed_layer = self.layer_idx
+            return key_states, value_states
 
+        self._lazy_evict()
         if gc is not None and c._streaming:
             for t in range(seq_new):
                 # with the fused decode the last token is quantised inside the decode launch
@@ -203,12 +220,24 @@ class CacheLayer(CacheLayerMixin):
             return self._keys, self._values
 
         if gc is not None:
-            if "decode_k" in gc:
-                gc["decode_k"] = torch.cat([gc["decode_k"], key_states], dim=2)
-                gc["decode_v"] = torch.cat([gc["decode_v"], value_states], dim=2)
-            else:
-                gc["decode_k"] = key_states
-                gc["decode_v"] = value_states
+            # tokens a non-streaming cache keeps as they are: appended in place to a buffer allocated
+            # ahead (doubling when full); gc["decode_k"] / ["decode_v"] are views of the rows in use
+            n = gc["decode_k"].shape[2] if "decode_k" in gc else 0
+            buf_k = gc.get("_dec_buf_k")
+            if buf_k is None or n + seq_new > buf_k.shape[2] or buf_k.dtype != key_states.dtype:
+                cap = max(c._decode_capacity, 2 * (n + seq_new))
+                B, nkv, _, hd = key_states.shape
+                new_k = torch.empty(B, nkv, cap, hd, dtype=key_states.dtype, device=key_states.device)
+                new_v = torch.empty(B, nkv, cap, hd, dtype=value_states.dtype, device=value_states.device)
+                if n:
+                    new_k[:, :, :n].copy_(gc["decode_k"])
+                    new_v[:, :, :n].copy_(gc["decode_v"])
+                buf_k, gc["_dec_buf_k"], gc["_dec_buf_v"] = new_k, new_k, new_v
+            buf_v = gc["_dec_buf_v"]
+            buf_k[:, :, n:n + seq_new].copy_(key_states)
+            buf_v[:, :, n:n + seq_new].copy_(value_states)
+            gc["decode_k"] = buf_k[:, :, :n + seq_new]
+            gc["decode_v"] = buf_v[:, :, :n + seq_new]
             self._seq_len += seq_new
             self._needs_decompress = True
             if fused:
@@ -233,8 +262,40 @@ class CacheLayer(CacheLayerMixin):
         pend = gc.pop("_pending", None) if gc is not None else None
         if pend is not None:
             k2, v2, slot = pend
+            k2 = k2.reshape(-1, k2.shape[-1]).contiguous()       # (nkv, hd)
+            v2 = v2.reshape(-1, v2.shape[-1]).contiguous()
             ops.stream_quantize(k2, v2, gc["signs"], get_codebook(k2.shape[-1], 8, k2.device),
                                 gc["k_idx_buf"], gc["v_idx_buf"], gc["k_norm_buf"], gc["v_norm_buf"], slot)
+
+    def _grow_stream(self, gc, k, need):
+        """(Re)allocate the stream buffers for at least `need` rows: the cache's decode capacity at
+        first, doubling afterwards (reference: src/shard/cache.py:220-230, which starts at 16 rows)."""
+        c = self._cache_ref
+        if c._stream_qjl:
+            raise NotImplementedError("the QJL residual is not part of the CUDA stream path")
+        if c._stream_bits != 8:
+            raise NotImplementedError("the CUDA stream quantizer emits 8-bit codes only")
+        B, heads, _, hd = k.shape
+        if B != 1:
+            raise NotImplementedError("one sequence per Cache (use one Cache per sequence)")
+        if k.dtype != torch.float16:
+            raise NotImplementedError("fp16 models only")
+        dev = k.device
+        if "signs" not in gc:
+            gc["signs"] = stream_signs(self.layer_idx, hd, dev)
+        cap = gc["k_idx_buf"].shape[0] if "k_idx_buf" in gc else 0
+        if need <= cap:
+            return
+        new_cap = max(need, c._decode_capacity if cap == 0 else cap * 2)
+        for key, shape, dtype in (("k_idx", (B, heads, hd), torch.uint8),
+                                  ("v_idx", (B, heads, hd), torch.uint8),
+                                  ("k_norm", (B, heads), torch.float16),
+                                  ("v_norm", (B, heads), torch.float16)):
+            new = torch.zeros((new_cap, *shape), device=dev, dtype=dtype)
+            old = gc.get(f"{key}_buf")
+            if old is not None:
+                new[: old.shape[0]].copy_(old)
+            gc[f"{key}_buf"] = new
 
     def _stream_append(self, k, v, position, defer=False):
         """Quantise one (1, nkv, 1, hd) token into the stream buffers
@@ -251,21 +312,9 @@ class CacheLayer(CacheLayerMixin):
         if B != 1:
             raise NotImplementedError("one sequence per Cache (use one Cache per sequence)")
         dev = k.device
-        if "signs" not in gc:
-            gc["signs"] = stream_signs(self.layer_idx, hd, dev)
         s = gc.get("stream_n", 0)
-        cap = gc["k_idx_buf"].shape[0] if "k_idx_buf" in gc else 0
-        if s + 1 > cap:
-            new_cap = max(s + 1, 16 if cap == 0 else cap * 2)
-            for key, shape, dtype in (("k_idx", (B, heads, hd), torch.uint8),
-                                      ("v_idx", (B, heads, hd), torch.uint8),
-                                      ("k_norm", (B, heads), torch.float16),
-                                      ("v_norm", (B, heads), torch.float16)):
-                new = torch.zeros((new_cap, *shape), device=dev, dtype=dtype)
-                old = gc.get(f"{key}_buf")
-                if old is not None:
-                    new[: old.shape[0]].copy_(old)
-                gc[f"{key}_buf"] = new
+        if "signs" not in gc or s >= gc["k_idx_buf"].shape[0]:
+            self._grow_stream(gc, k, s + 1)
         k2 = k.reshape(heads, hd)
         v2 = v.reshape(heads, hd)
         if k2.dtype != torch.float16:
@@ -322,8 +371,11 @@ class Cache(HFCache):
     def __init__(self, head_dim=128, num_layers=32, n_kv_heads=8, device="cuda",
                  k_target_cr=20.0, max_rank_k=192,
                  v_vq_group_size=4, v_vq_codebook_size=256,
-                 sink_tokens=4, residual_window=64, rope_inv_freq=None):
+                 sink_tokens=4, residual_window=64, rope_inv_freq=None, decode_capacity=256):
         self.head_dim = head_dim
+        # rows the per-layer buffers of decoded tokens (8-bit stream, fp16 decode buffer) are
+        # allocated for when the cache is compressed; they double when they run full
+        self._decode_capacity = max(16, int(decode_capacity))
         self._num_layers = num_layers
         self._n_kv_heads = n_kv_heads
         self._per_layer_dim = n_kv_heads * head_dim

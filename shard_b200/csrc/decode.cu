@@ -191,6 +191,7 @@ static int check_shape(const ShardDecodeShape* sh) {
   if (sh->n_comp < 0 || sh->tok_begin < 0 || sh->tok_end < sh->tok_begin || sh->tok_end > sh->n_comp)
     return SHARD_E_ARG;
   if (sh->n_sink < 0 || sh->n_win < 0 || sh->n_stream < 0 || sh->n_dec < 0) return SHARD_E_ARG;
+  if (sh->dec_cap != 0 && sh->dec_cap < sh->n_dec) return SHARD_E_ARG;
   if ((sh->tok_end - sh->tok_begin) + sh->n_sink + sh->n_win + sh->n_dec + sh->n_stream <= 0) return SHARD_E_ARG;
   return SHARD_OK;
 }

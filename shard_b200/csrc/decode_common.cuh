@@ -140,7 +140,7 @@ __device__ __forceinline__ void process_rows(SoftmaxState& st, const ShardSeq& s
     if (u < n_fp) {
       const bool in_sink = u < sh.n_sink, in_dec = u >= n_sw;
       const int r = in_sink ? u : (in_dec ? u - n_sw : u - sh.n_sink);
-      const int rows = in_sink ? sh.n_sink : (in_dec ? sh.n_dec : sh.n_win);
+      const int rows = in_sink ? sh.n_sink : (in_dec ? (sh.dec_cap > 0 ? sh.dec_cap : sh.n_dec) : sh.n_win);
       const __half* kb = reinterpret_cast<const __half*>(in_sink ? sq.sink_k : (in_dec ? sq.dec_k : sq.win_k));
       const __half* vb = reinterpret_cast<const __half*>(in_sink ? sq.sink_v : (in_dec ? sq.dec_v : sq.win_v));
       const size_t off = ((size_t)kv * rows + r) * HD + 4 * lane;

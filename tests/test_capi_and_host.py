@@ -36,7 +36,7 @@ def test_struct_layouts_match_header():
     import ctypes as C
     from shard_b200 import _lib
     assert C.sizeof(_lib.ShardSeq) == 21 * 8
-    assert C.sizeof(_lib.ShardDecodeShape) == 14 * 4
+    assert C.sizeof(_lib.ShardDecodeShape) == 15 * 4
 
 
 def test_argument_validation_without_gpu():
