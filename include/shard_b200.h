@@ -294,12 +294,18 @@ int shard_b200_undo_rope(const void* k_f16, int64_t head_stride, int64_t tok_str
                          void* stream);
 
 /*
- * proj[n][keep] = (flat - mean) @ w, fp32: the PCA projection of
- * Cache._compress_k (src/shard/cache.py:392).  flat: [n][dim], mean: [dim],
- * w: [dim][keep] (= int8 basis * fp32 scale).  dim must be a multiple of 16.
+ * proj[n][keep] = (flat - mean) @ w: the PCA projection of Cache._compress_k
+ * (src/shard/cache.py:392), on the tensor cores with fp32 accuracy (every operand is split into
+ * a tf32 head and tail; three tf32 products per k-step accumulate in fp32).
+ * flat: [n][dim], mean: [dim], w: [dim][keep] (= int8 basis * fp32 scale), all fp32, 16-byte
+ * aligned; dim a multiple of 32, at most 1024; keep even, at most 192.  workspace:
+ * shard_b200_k_project_workspace_bytes(dim, keep) bytes, 16-byte aligned (a status word that a
+ * bounded wait inside the kernel sets to 1 when it gives up, then the split weights).
  */
+size_t shard_b200_k_project_workspace_bytes(int32_t dim, int32_t keep);
 int shard_b200_k_project(const float* flat, const float* mean, const float* w, int32_t n, int32_t dim,
-                         int32_t keep, float* proj_out, void* stream);
+                         int32_t keep, float* proj_out, void* workspace, size_t workspace_bytes,
+                         void* stream);
 
 /* Scratch bytes for shard_b200_k_quantize_pack. */
 size_t shard_b200_k_quantize_workspace_bytes(int32_t n, int32_t keep);

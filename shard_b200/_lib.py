@@ -67,8 +67,9 @@ _SIGNATURES = {
                                             C.c_int32, C.c_void_p, C.c_void_p]),
     "shard_b200_undo_rope": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
                                        C.c_void_p, C.c_void_p, C.c_void_p]),
+    "shard_b200_k_project_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
     "shard_b200_k_project": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
-                                       C.c_void_p, C.c_void_p]),
+                                       C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "shard_b200_k_quantize_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
     "shard_b200_k_quantize_pack": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p,
                                              C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),

@@ -16,19 +16,38 @@ from ._lib import ShardSeq, ptr
 from .streaming import get_codebook
 
 GQA = 4
+# a forward over more new tokens than this after compression takes the dequantised path (one launch
+# per query token would no longer pay)
+MAX_FUSED_QUERY_TOKENS = 256
 
 
 def _phase_for(cache, gc, pos_q, tok_begin, tok_end, dev):
     """cos/sin table of the step; all layers of a step share positions, so it is
-    computed by the first layer that asks and reused by the others."""
+    computed by the first layer that asks and reused by the others.  A forward over several
+    new tokens needs one table per query position: `cache._phase_keep` tables are kept then
+    (least recently made first out)."""
     key = (int(pos_q), gc["compress_start"], tok_begin, tok_end)
-    if cache._phase_key != key:
+    if cache._phase_key == key:
+        return cache._phase
+    tabs = getattr(cache, "_phase_tabs", None)
+    if tabs is None:
+        tabs = cache._phase_tabs = {}
+    tab = tabs.get(key)
+    if tab is None:
         n = tok_end - tok_begin
-        if cache._phase is None or cache._phase.numel() < ops.phase_table_numel(n):
-            cache._phase = torch.empty(ops.phase_table_numel(n), dtype=torch.float16, device=dev)
-        ops.phase_table(gc["compress_start"] + tok_begin, pos_q, n, cache._inv_freq(dev), out=cache._phase)
-        cache._phase_key = key
-    return cache._phase
+        need = ops.phase_table_numel(n)
+        keep = max(1, int(getattr(cache, "_phase_keep", 1)))
+        tab = None
+        while len(tabs) >= keep:                       # reuse the oldest table's memory
+            old = tabs.pop(next(iter(tabs)))
+            if tab is None and old.numel() >= need and old.device == dev:
+                tab = old
+        if tab is None:
+            tab = torch.empty(need, dtype=torch.float16, device=dev)
+        ops.phase_table(gc["compress_start"] + tok_begin, pos_q, n, cache._inv_freq(dev), out=tab)
+        tabs[key] = tab
+    cache._phase, cache._phase_key = tab, key
+    return tab
 
 
 def _seq_record(gc, dev):
@@ -93,14 +112,16 @@ def _launch_state(gc, cache, dev, nkv, n_q, t0, t1, with_fp16_segments, partial_
 
 
 def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_fp16_segments=True, out=None,
-                 push=None):
+                 push=None, visible_new=None):
     """Run the fused decode for one layer.
 
     q_rope: (1, n_q, 1, 128) fp16 CUDA.  `tok_range` limits the middle segment to
     [begin, end) (sequence-split mode); `partial_out` returns the fp32
     (n_q, 132) record (max, sum-exp, 0, 0, acc[128]) instead of fp16 attention.
     `push` (a `parallel.PeerExchange`, with `partial_out`) makes the launch deliver that
-    record into every rank's exchange buffer itself.
+    record into every rank's exchange buffer itself.  `visible_new` limits the decoded tokens
+    (streamed rows, or rows of the fp16 decode buffer) the query attends to, to the first
+    `visible_new` of them: the causal mask of a forward over several new tokens.
 
     A bounded wait that gives up inside the kernel leaves a status word in the cache's
     workspace; `Cache.check()` reads it (once per step or request, it synchronises).
@@ -126,6 +147,8 @@ def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_f
         raise _lib.ShardError(f"tensor lives on cuda:{ls.dev_index} but the current device is cuda:{cur}; "
                               "make the tensor's device current (torch.cuda.device) before the call")
     n_stream = gc.get("stream_n", 0) if with_fp16_segments else 0
+    if visible_new is not None and n_stream > 0:
+        n_stream = min(n_stream, int(visible_new))
     pending = gc.pop("_pending", None)
     if pending is not None and (not with_fp16_segments or pending[2] != n_stream - 1):
         gc["_pending"] = pending
@@ -152,6 +175,8 @@ def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_f
             dk, dv = gc["decode_k"], gc["decode_v"] = dk.contiguous(), dv.contiguous()
         n_dec = dk.shape[2]
         dec_cap = dk.stride(1) // hd if nkv > 1 else n_dec   # rows allocated per KV head
+        if visible_new is not None:
+            n_dec = min(n_dec, int(visible_new))
         seq.dec_k, seq.dec_v = dk.data_ptr(), dv.data_ptr()
     q2 = q_rope
     if q2.stride(3) != 1 or q2.stride(1) != hd:
@@ -186,20 +211,48 @@ def decode_layer(q_rope, layer, pos_q, tok_range=None, partial_out=False, with_f
 
 
 def fused_attention_compressed(q_rope, layer, pos_q, inv_freq=None, attn_mask=None, out=None):
-    """Attention of one query token over the layer's compressed cache; returns
-    (1, n_q, 1, hd) in q's dtype, or None if the layer is not compressed.
+    """Attention of the new query token(s) over the layer's compressed cache; returns
+    (1, n_q, s, hd) in q's dtype, or None if the layer is not compressed.
 
-    `attn_mask` is accepted for signature compatibility: for a single trailing
-    query of one sequence the causal mask is identically zero (the reference's own
-    fused variant skips it for the same reason, src/shard/attention.py:254).
-    `inv_freq` is taken from the cache the layer belongs to.  `out` (not in the reference's
-    signature) lets the caller name a contiguous (1, n_q, 1, hd) fp16 tensor to write into.
+    One query token (s = 1, the decode step) is one kernel launch.  For s > 1 -- a forward over
+    several new tokens after compression, which the reference serves by dequantising the whole
+    cache (src/shard/attention.py:357-362, src/shard/cache.py:87-124) -- `pos_q` is the position
+    of the LAST query; query j attends to everything before the s new tokens plus the first j + 1
+    of them (causal), one launch per query token, nothing dequantised.  The new tokens must
+    already have been appended (`update`).
+
+    `attn_mask` is accepted for signature compatibility: for one sequence without padding the
+    causal mask is what the above implements (the reference's own fused variant skips it for the
+    same reason, src/shard/attention.py:254).  `inv_freq` is taken from the cache the layer
+    belongs to.  `out` (not in the reference's signature) lets the caller name a contiguous
+    (1, n_q, s, hd) fp16 tensor to write into.
     """
     gc = getattr(layer, "_gpu_compressed", None)
     if gc is None:
         return None
-    out = decode_layer(q_rope, layer, pos_q, out=None if out is None else out.view(q_rope.shape[1], q_rope.shape[3]))
-    return out.view(1, q_rope.shape[1], 1, q_rope.shape[3])
+    _, n_q, s_q, hd = q_rope.shape
+    if s_q == 1:
+        res = decode_layer(q_rope, layer, pos_q, out=None if out is None else out.view(n_q, hd))
+        return res.view(1, n_q, 1, hd)
+    cache = layer._cache_ref
+    layer._flush_pending()                             # every new token is in its row before the first query looks
+    n_new_total = gc.get("stream_n", 0) if "k_idx_buf" in gc else (gc["decode_k"].shape[2] if "decode_k" in gc else 0)
+    if n_new_total < s_q:
+        raise _lib.ShardError("append the new tokens (update) before attending with them")
+    res = torch.empty(s_q, n_q, hd, dtype=torch.float16, device=q_rope.device)
+    prev_keep = getattr(cache, "_phase_keep", 1)
+    cache._phase_keep = max(prev_keep, min(s_q, 8))    # the layers of this forward share the tables
+    try:
+        for j in range(s_q):
+            decode_layer(q_rope[:, :, j:j + 1, :], layer, pos_q - (s_q - 1) + j, out=res[j],
+                         visible_new=n_new_total - (s_q - 1) + j)
+    finally:
+        cache._phase_keep = prev_keep
+    res = res.permute(1, 0, 2).unsqueeze(0)            # (1, n_q, s, hd)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
 
 
 def enable_llama_fused_attention(model=None):
@@ -221,13 +274,19 @@ def enable_llama_fused_attention(model=None):
                 past_key_values=None, **kwargs):
         cache = past_key_values
         layer = cache.layers[self.layer_idx] if isinstance(cache, Cache) else None
+        bsz, q_len = hidden_states.shape[:2]
+        if (layer is not None and self.layer_idx == 0 and not cache._compressed and layer._prefilled
+                and bsz == 1 and cache._rope_inv_freq is not None):
+            # the first forward after the prefill: the reference compresses inside layer 0's update and
+            # serves that layer from the dequantised cache once; compressing before layer 0 attends
+            # lets every layer of this step take the fused kernel
+            cache.compress()
         use_fused = (layer is not None and layer._gpu_compressed is not None
-                     and hidden_states.shape[1] == 1 and hidden_states.shape[0] == 1
+                     and 1 <= q_len <= MAX_FUSED_QUERY_TOKENS and bsz == 1
                      and cache._rope_inv_freq is not None)
         if not use_fused:
             return stock_forward(self, hidden_states, position_embeddings=position_embeddings,
                                  attention_mask=attention_mask, past_key_values=past_key_values, **kwargs)
-        bsz, q_len = hidden_states.shape[:2]
         shape = (bsz, q_len, -1, self.head_dim)
         q = self.q_proj(hidden_states).view(shape).transpose(1, 2)
         k = self.k_proj(hidden_states).view(shape).transpose(1, 2)

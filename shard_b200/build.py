@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libshard_b200.so")
-SOURCES = ["decode.cu", "decode_pipe.cu", "stream.cu", "compress.cu", "peer.cu"]
+SOURCES = ["decode.cu", "decode_pipe.cu", "stream.cu", "compress.cu", "project.cu", "peer.cu"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

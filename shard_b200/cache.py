@@ -32,6 +32,35 @@ KERNEL_RANK_STEP = 32
 KERNEL_MAX_RANK = 192
 
 
+def pca_fit(flat, mean, rank):
+    """Top-`rank` principal directions of the rows of `flat` (n, p) around `mean`: the
+    eigenvectors of the p x p covariance, largest eigenvalue first, and those eigenvalues.
+
+    Replaces the reference's randomised `torch.svd_lowrank(flat - mean, q=rank, niter=24)`
+    (src/shard/cache.py:376: 48 passes over the n x p matrix) by one pass -- the Gram matrix
+    (flat - mean)^T (flat - mean), a p x p x n contraction in fp32 -- and a symmetric
+    eigensolver on the small p x p matrix.  The subspace is the exact optimum the randomised
+    method approximates, so it captures at least as much variance; individual vectors differ
+    in sign and, within near-equal eigenvalues, by rotations, which the rest of the path is
+    indifferent to (the basis is an input of everything downstream).
+    """
+    n, p = flat.shape
+    xc = flat - mean
+    # full-precision fp32 products whatever the global TF32 switch says: the trailing
+    # eigenvalues are 1e-4 of the leading ones and decide the bit allocation
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        gram = xc.T @ xc
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    evals, evecs = torch.linalg.eigh(gram)
+    order = torch.arange(p - 1, p - 1 - rank, -1, device=flat.device)
+    basis = evecs[:, order].contiguous()
+    eigvals = (evals[order].clamp(min=0) / n).float()
+    return basis, eigvals
+
+
 def hadamard(x):
     """Normalised Walsh-Hadamard transform on the last dim (self-inverse).
 
@@ -391,6 +420,9 @@ class Cache(HFCache):
         self._stream_qjl = False
         self._lazy_per_layer = True
         self._full_fused = False
+        # how the PCA basis of the keys is fitted: "eigh" (covariance + symmetric eigensolver on the
+        # GPU) or "svd_lowrank" (the reference's randomised call)
+        self._k_pca = "eigh"
         self._last_accessed_layer = -1
         self._compressed = False
         self._device = device
@@ -472,10 +504,13 @@ class Cache(HFCache):
         n, p = flat.shape
         mean = flat.mean(dim=0)
         rank = min(self._max_rank_k, p, n - 1)
-        if basis is None:
+        if basis is None and self._k_pca == "svd_lowrank":
+            # the reference's own call (src/shard/cache.py:376): randomised, 24 power iterations
             _, S, V = torch.svd_lowrank(flat - mean, q=rank, niter=24)
             basis = V[:, :rank]
             eigvals = (S[:rank].float() ** 2) / n
+        elif basis is None:
+            basis, eigvals = pca_fit(flat, mean, rank)
         else:
             basis = basis.to(dev, torch.float32)[:, :rank]
             eigvals = ((flat - mean) @ basis).pow(2).sum(dim=0) / n

@@ -1,4 +1,4 @@
-// Prefill compressor kernels: RoPE removal, PCA projection, the two-stage int4
+// Prefill compressor kernels: RoPE removal, the two-stage int4
 // quantiser with nibble packing, Hadamard + per-channel normalisation of V and
 // nearest-centroid VQ assignment.
 //
@@ -33,59 +33,6 @@ __global__ void __launch_bounds__(128) undo_rope_kernel(const __half* __restrict
     o[i] = __fadd_rn(__fmul_rn(lo, cs), __fmul_rn(hi, sn));
     o[i + 64] = __fsub_rn(__fmul_rn(hi, cs), __fmul_rn(lo, sn));
   }
-}
-
-// ---------------------------------------------------------------------------
-// PCA projection: proj[n][keep] = (flat - mean) @ w, fp32 FMA accumulation
-// ---------------------------------------------------------------------------
-constexpr int PJ_BM = 64, PJ_BN = 64, PJ_BK = 16;
-
-__global__ void __launch_bounds__(256) k_project_kernel(const float* __restrict__ flat,
-                                                        const float* __restrict__ mean,
-                                                        const float* __restrict__ w, int n, int dim, int keep,
-                                                        float* __restrict__ proj) {
-  __shared__ float As[PJ_BK][PJ_BM + 4];
-  __shared__ float Bs[PJ_BK][PJ_BN + 4];
-  const int tid = threadIdx.x;
-  const int m0 = blockIdx.x * PJ_BM, n0 = blockIdx.y * PJ_BN;
-  const int tm = (tid >> 4) * 4, tn = (tid & 15) * 4;
-  float acc[4][4] = {};
-  for (int k0 = 0; k0 < dim; k0 += PJ_BK) {
-    {  // A tile: 64 rows x 16 k; thread loads 4 consecutive k of one row
-      const int r = tid >> 2, kk = (tid & 3) * 4;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (m0 + r < n) {
-        v = *reinterpret_cast<const float4*>(flat + (size_t)(m0 + r) * dim + k0 + kk);
-        const float4 mu = *reinterpret_cast<const float4*>(mean + k0 + kk);
-        v.x = __fsub_rn(v.x, mu.x); v.y = __fsub_rn(v.y, mu.y);
-        v.z = __fsub_rn(v.z, mu.z); v.w = __fsub_rn(v.w, mu.w);
-      }
-      As[kk + 0][r] = v.x; As[kk + 1][r] = v.y; As[kk + 2][r] = v.z; As[kk + 3][r] = v.w;
-    }
-    {  // B tile: 16 k x 64 cols
-      const int kk = tid >> 4, c = (tid & 15) * 4;
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        Bs[kk][c + j] = (n0 + c + j < keep) ? w[(size_t)(k0 + kk) * keep + n0 + c + j] : 0.f;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int kk = 0; kk < PJ_BK; ++kk) {
-      const float4 a = *reinterpret_cast<const float4*>(&As[kk][tm]);
-      const float4 b = *reinterpret_cast<const float4*>(&Bs[kk][tn]);
-      const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
-    }
-    __syncthreads();
-  }
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (m0 + tm + i < n && n0 + tn + j < keep) proj[(size_t)(m0 + tm + i) * keep + n0 + tn + j] = acc[i][j];
 }
 
 // ---------------------------------------------------------------------------
@@ -302,17 +249,6 @@ extern "C" int shard_b200_undo_rope(const void* k_f16, int64_t head_stride, int6
   if (n == 0) return SHARD_OK;
   undo_rope_kernel<<<n, 128, 0, (cudaStream_t)stream>>>((const __half*)k_f16, head_stride, tok_stride, nkv, n,
                                                          pos_start, inv_freq, flat_out);
-  SHARD_CHECK_LAUNCH();
-  return SHARD_OK;
-}
-
-extern "C" int shard_b200_k_project(const float* flat, const float* mean, const float* w, int32_t n, int32_t dim,
-                                    int32_t keep, float* proj_out, void* stream) {
-  if (!flat || !mean || !w || !proj_out || n < 0 || keep < 1 || dim < 16 || (dim % 16)) return SHARD_E_ARG;
-  if (((uintptr_t)flat | (uintptr_t)mean) & 15) return SHARD_E_ALIGN;
-  if (n == 0) return SHARD_OK;
-  dim3 grid((n + PJ_BM - 1) / PJ_BM, (keep + PJ_BN - 1) / PJ_BN);
-  k_project_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(flat, mean, w, n, dim, keep, proj_out);
   SHARD_CHECK_LAUNCH();
   return SHARD_OK;
 }

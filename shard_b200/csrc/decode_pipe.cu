@@ -79,9 +79,6 @@ __device__ __forceinline__ void umma_ts_1t(uint32_t d_tmem, uint32_t a_tmem, uin
 __device__ __forceinline__ void umma_commit_1t(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 // Plain barrier among a subset of the CTA's warps (id 1..15, `count` threads).
 __device__ __forceinline__ void named_bar_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");

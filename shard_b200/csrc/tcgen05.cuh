@@ -28,16 +28,6 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity, uint32_t
       : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
   return ok != 0;
 }
-// non-blocking test: has the phase with this parity completed?
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
 // bounded wait: returns false (and raises *abort_flag) if the phase does not complete within
 // TC_WAIT_TRIES attempts of up to TC_WAIT_HINT_NS each (tens of milliseconds in total; a tile
 // takes microseconds)
@@ -47,6 +37,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try(bar, parity, TC_WAIT_HINT_NS)) return true;
   *abort_flag = 1;
   return false;
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // Programmatic dependent launch.  `griddep_launch` lets the next kernel in the stream (if it was
 // launched with the programmatic-serialization attribute) place its CTAs on SMs as they become

@@ -68,13 +68,18 @@ def undo_rope(k, pos_start, inv_freq):
 
 
 def k_project(flat, mean, w):
-    """(flat - mean) @ w in fp32; flat (n, dim), mean (dim,), w (dim, keep)."""
+    """(flat - mean) @ w with fp32 accuracy on the tensor cores; flat (n, dim), mean (dim,), w (dim, keep)."""
     require_cuda(flat, mean, w)
     n, dim = flat.shape
     keep = w.shape[1]
+    lib = _lib.load()
+    wsb = lib.shard_b200_k_project_workspace_bytes(dim, keep)
+    if wsb == 0:
+        raise _lib.ShardError(f"k_project supports dim % 32 == 0, dim <= 1024, even keep <= 192 (got {dim}, {keep})")
+    ws = torch.empty(wsb, dtype=torch.uint8, device=flat.device)
     proj = torch.empty(n, keep, dtype=torch.float32, device=flat.device)
-    check(_lib.load().shard_b200_k_project(ptr(_c(flat, torch.float32)), ptr(_c(mean, torch.float32)),
-                                           ptr(_c(w, torch.float32)), n, dim, keep, ptr(proj), cur_stream()),
+    check(lib.shard_b200_k_project(ptr(_c(flat, torch.float32)), ptr(_c(mean, torch.float32)),
+                                   ptr(_c(w, torch.float32)), n, dim, keep, ptr(proj), ptr(ws), wsb, cur_stream()),
           "k_project")
     return proj
 

@@ -102,6 +102,36 @@ def decode_buffer_fixture(rc, ra, inv_freq):
          dec_q=t2n(torch.cat(qs, 2)), dec_out=t2n(torch.cat(outs, 2)))
 
 
+def multi_token_fixture(rc, inv_freq):
+    """configs[0] cache, then an 8-token continuation in ONE forward, the way the reference serves
+    it (hidden_states.shape[1] > 1 after compression, src/shard/attention.py:357-362): `update`
+    appends the tokens and returns the fully dequantised K / V (`_ensure_dequant`,
+    src/shard/cache.py:87-124), and the stock attention runs over them with a causal mask.  Both
+    append modes: the 8-bit stream and the default fp16 decode buffer."""
+    import math
+    out = {}
+    g = torch.Generator().manual_seed(909)
+    k_new = torch.randn(1, 8, 8, 128, generator=g).half()
+    v_new = torch.randn(1, 8, 8, 128, generator=g).half()
+    q_new = torch.randn(1, 32, 8, 128, generator=g).half()
+    for tag, streaming in (("st", True), ("dec", False)):
+        k, v, q = synth.make_kvq(2048, 0)
+        cache = build_cache(rc, k, v, inv_freq, streaming=streaming)
+        cache.compress()
+        layer = cache.layers[0]
+        keys, values = layer.update(k_new, v_new)                  # non-fused update: full dequantised K / V
+        assert keys.shape == (1, 8, 2048 + 8, 128)
+        kk = keys.float().repeat_interleave(4, dim=1)
+        vv = values.float().repeat_interleave(4, dim=1)
+        sc = torch.einsum("bhsd,bhkd->bhsk", q_new.float(), kk) / math.sqrt(128)
+        mask = torch.full((8, 2048 + 8), float("-inf"))
+        for j in range(8):
+            mask[j, : 2048 + j + 1] = 0.0
+        w = torch.softmax(sc + mask, dim=-1)
+        out[tag + "_out"] = t2n(torch.einsum("bhsk,bhkd->bhsd", w, vv).half())
+    save("cfg0_multi.npz", k_new=t2n(k_new), v_new=t2n(v_new), q_new=t2n(q_new), **out)
+
+
 def main(ref_root, only=None):
     rc = load_reference(ref_root)
     import shard.attention as ra
@@ -113,6 +143,9 @@ def main(ref_root, only=None):
     inv_freq = synth.rope_inv_freq()
     if only == "decbuf":
         decode_buffer_fixture(rc, ra, inv_freq)
+        return
+    if only == "multi":
+        multi_token_fixture(rc, inv_freq)
         return
 
     # ---- Lloyd-Max codebook, signs, inv_freq --------------------------------
@@ -276,9 +309,10 @@ def main(ref_root, only=None):
          mem_stream=np.array([cache.memory_bytes(), cache.clean_memory_bytes(),
                               cache.fp16_equivalent_bytes()], np.int64))
     decode_buffer_fixture(rc, ra, inv_freq)
+    multi_token_fixture(rc, inv_freq)
 
 
 if __name__ == "__main__":
     if len(sys.argv) not in (2, 3):
-        sys.exit("usage: make_golden.py <reference checkout> [decbuf]")
+        sys.exit("usage: make_golden.py <reference checkout> [decbuf|multi]")
     main(sys.argv[1], sys.argv[2] if len(sys.argv) == 3 else None)

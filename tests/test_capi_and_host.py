@@ -56,6 +56,9 @@ def test_argument_validation_without_gpu():
     seq = _lib.ShardSeq()
     assert lib.shard_b200_decode_attn(C.addressof(seq), 1, C.byref(sh), None, None, None, 0, None) == -1
     assert lib.shard_b200_k_quantize_pack(None, None, 10, 4, None, None, None, 0, None) == -1
+    assert lib.shard_b200_k_project_workspace_bytes(1024, 192) == 16 + 32 * 2 * 192 * 128
+    assert lib.shard_b200_k_project_workspace_bytes(1000, 192) == 0 and lib.shard_b200_k_project_workspace_bytes(1024, 194) == 0
+    assert lib.shard_b200_k_project(None, None, None, 10, 1024, 64, None, None, 0, None) == -1
     assert lib.shard_b200_lse_merge(None, 2, 32, None, None) == -1
     # sequence-split exchange: buffer = flags (2 slots x world x nkv u32, rounded to 256 B) + 2 slots of records
     assert lib.shard_b200_peer_buffer_bytes(2, 8) == 256 + 2 * 2 * 32 * 132 * 4

@@ -78,7 +78,7 @@ try:
     decode_layer(q_o, full, 5100)            # tensors of two different devices in one call
     raise SystemExit("a tensor of another device was accepted")
 except Exception as e:
-    assert "current device" in str(e), e
+    assert "cuda:" in str(e) and ("current device" in str(e) or "lives on" in str(e)), e
 dist.barrier()
 dist.destroy_process_group()
 print("ok", rank)
@@ -96,4 +96,4 @@ def test_sequence_split_decode_over_nccl(tmp_path):
                               stdout=subprocess.PIPE, stderr=subprocess.PIPE) for r in range(2)]
     for p in procs:
         out, err = p.communicate(timeout=300)
-        assert p.returncode == 0, err.decode()[-3000:]
+        assert p.returncode == 0, err.decode()[-1500:]

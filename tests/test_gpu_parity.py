@@ -108,6 +108,67 @@ def test_k_project(ops):
     assert np.allclose(N(proj), g["p_proj"], atol=3e-5, rtol=1e-5)
 
 
+def test_k_project_full_size_against_float64(ops):
+    """The tensor-core projection (split tf32 operands, three products per k-step) at the size of a
+    32K-token layer, against the float64 product and beside PyTorch's fp32 (FMA) product."""
+    g = torch.Generator(device=DEV).manual_seed(5)
+    n, dim, keep = 32700, 1024, 192
+    flat = torch.randn(n, dim, generator=g, device=DEV) * 2.0 + 0.3
+    mean = flat.mean(dim=0)
+    basis, _ = torch.linalg.qr(torch.randn(dim, keep, generator=g, device=DEV))
+    w = ((basis / (basis.abs().amax(0) / 127)).round().clamp(-127, 127) * (basis.abs().amax(0) / 127)).contiguous()
+    proj = ops.k_project(flat, mean.contiguous(), w)
+    ref64 = ((flat.double() - mean.double()) @ w.double())
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    fma = (flat - mean) @ w
+    torch.backends.cuda.matmul.allow_tf32 = prev
+    err_tc = (proj.double() - ref64).abs().max().item()
+    err_fma = (fma.double() - ref64).abs().max().item()
+    print(f"\nk_project n={n}: max |tc - f64| = {err_tc:.3e}, max |fp32 fma - f64| = {err_fma:.3e}, "
+          f"max |value| = {ref64.abs().max().item():.2f}")
+    assert err_tc <= 2e-5
+    assert err_tc <= 4 * err_fma + 1e-6
+    # ragged tail: the last tile has 60 live rows; an odd multiple of 16 columns
+    proj2 = ops.k_project(flat[:444], mean.contiguous(), w[:, :176].contiguous())
+    assert torch.allclose(proj2.double(), ref64[:444, :176], atol=2e-5, rtol=0)
+
+
+def test_int4_codes_from_tensor_core_projection(ops):
+    """Codes computed from the tensor-core projection against codes from an fp32 (FMA) projection of
+    the same keys: the two products differ in their last bits (as any two summation orders do, the
+    reference's own CPU and GPU products included), so a code may differ where a value sits on a
+    rounding boundary.  The count is reported, and every differing code is shown to sit there."""
+    import synth
+    k, v, q = synth.make_kvq(2048, 0)
+    inv = synth.rope_inv_freq().to(DEV)
+    flat = ops.undo_rope(k.to(DEV)[0, :, 4:1984, :], 4, inv)
+    mean = flat.mean(dim=0).contiguous()
+    from shard_b200.cache import pca_fit
+    basis, eig = pca_fit(flat, mean, 192)
+    scale = basis.abs().amax(0).clamp(min=1e-6) / 127.0
+    w = ((basis / scale).round().clamp(-127, 127) * scale).contiguous()
+    proj_tc = N(ops.k_project(flat, mean, w))
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    proj_fma = N((flat - mean) @ w)
+    torch.backends.cuda.matmul.allow_tf32 = prev
+    proj64 = N((flat.double() - mean.double()) @ w.double())
+    alloc = [4] * 192
+    q_tc, cs_tc, _ = O.k_int4_codes(proj_tc, alloc)
+    q_fma, cs_fma, _ = O.k_int4_codes(proj_fma, alloc)
+    diff = np.argwhere(q_tc != q_fma)
+    print(f"\nint4 codes: {len(diff)} of {q_tc.size} differ between the tensor-core and the fp32-FMA projection")
+    assert len(diff) <= 2e-3 * q_tc.size
+    assert np.abs(q_tc.astype(int) - q_fma.astype(int)).max() <= 1
+    for r, c in diff[:200]:
+        col = proj64[:, c]
+        lo, rng = col.min(), col.max() - col.min()
+        u = (col[r] - lo) / rng * 15.0
+        # on a stage-1 rounding boundary (half-integer) to within the products' last bits
+        assert abs((u % 1.0) - 0.5) < 2e-4, (r, c, u)
+
+
 @pytest.mark.parametrize("tag", ["a", "b", "c", "d"])
 def test_k_quantize_pack_bit_exact(ops, tag):
     g = load_golden("kquant.npz")
@@ -266,6 +327,47 @@ def test_decode_with_fp16_decode_buffer_against_reference(ops, codebook, golden_
     out = _decode(layer, d["dec_q"][0, :, 2, :], 2060)
     exact, *_ = O.attention_exact(d["dec_q"][0, :, 2, :], gc_np, 2060, O.default_inv_freq(), stream=stream, decode=dec)
     assert tol_ok(out, exact, atol=EXACT_ATOL, rtol=EXACT_RTOL)
+
+
+@pytest.mark.parametrize("mode", ["st", "dec"])
+def test_multi_token_forward_after_compression_against_reference(golden_cfg0, mode):
+    """Eight new tokens in one forward after compression.  The reference appends them and runs the
+    stock attention over the fully dequantised cache with a causal mask; here every query token is
+    one fused launch that sees the first j + 1 of the new tokens -- nothing is dequantised.  Both
+    append modes (8-bit stream, fp16 decode buffer) against the reference's outputs, and against
+    the float64 evaluation of the same cache."""
+    from gpu_helpers import layer_from_golden
+    from shard_b200 import Cache, fused_attention_compressed
+    g, d = golden_cfg0, load_golden("cfg0_multi.npz")
+    fake, gc_np = layer_from_golden(g)
+    inv = torch.from_numpy(O.default_inv_freq())
+    cache = Cache(num_layers=1, rope_inv_freq=inv)
+    cache._streaming = mode == "st"
+    cache._compressed = True
+    layer = cache.layers[0]
+    layer._gpu_compressed = fake._gpu_compressed
+    layer._prefilled, layer._seq_len, layer._needs_decompress = True, 2048, True
+    layer._ensure_dequant = lambda: pytest.fail("the fused multi-token path must not dequantise the cache")
+    k_new, v_new, q_new = T(d["k_new"]), T(d["v_new"]), T(d["q_new"])
+    cache._fused_decode_update = True
+    layer.update(k_new, v_new)
+    cache._fused_decode_update = False
+    assert layer.get_seq_length() == 2056
+    out = N(fused_attention_compressed(q_new, layer, 2055, inv, None))
+    assert out.shape == (1, 32, 8, 128)
+    ref = d[mode + "_out"]
+    assert tol_ok(out, ref), np.abs(out.astype(np.float32) - ref.astype(np.float32)).max()
+    cb = O.lloyd_max_codebook(128, 8)
+    for j in (0, 3, 7):
+        kw = {}
+        if mode == "st":
+            ki, kn, vi, vn = O.stream_quantize(np.moveaxis(d["k_new"][0], 1, 0)[:j + 1], np.moveaxis(d["v_new"][0], 1, 0)[:j + 1],
+                                               O.stream_signs(0), cb)
+            kw["stream"] = dict(k_idx=ki, v_idx=vi, k_norm=kn, v_norm=vn, signs=O.stream_signs(0), codebook=cb)
+        else:
+            kw["decode"] = (d["k_new"][0][:, :j + 1], d["v_new"][0][:, :j + 1])
+        exact, *_ = O.attention_exact(d["q_new"][0, :, j, :], gc_np, 2048 + j, O.default_inv_freq(), **kw)
+        assert tol_ok(out[0, :, j, :], exact, atol=EXACT_ATOL, rtol=EXACT_RTOL)
 
 
 def _check_random(n_comp, rank, n_sink, n_win, pos_q, compress_start=None, n_stream=0, seed=0, ops=None,
@@ -478,8 +580,14 @@ def test_cache_compress_and_decode_end_to_end(ops):
     stream = dict(k_idx=N(gc["k_idx_buf"][:1, 0]), v_idx=N(gc["v_idx_buf"][:1, 0]),
                   k_norm=N(gc["k_norm_buf"][:1, 0]), v_norm=N(gc["v_norm_buf"][:1, 0]),
                   signs=N(gc["signs"]), codebook=O.lloyd_max_codebook(128, 8))
+    # the float64 evaluation of this dictionary is the tight bar; the emulation of the reference's fp16
+    # arithmetic is itself up to 4e-3 away from it on these outlier-channel values (outputs up to 2.4),
+    # so against it the reference bar is asked of 99.9 % of the elements and 1.5x of it of all
+    exact, *_ = O.attention_exact(N(qt)[0, :, 0, :], gc_np, 1024, O.default_inv_freq(), stream=stream)
+    assert tol_ok(N(out)[0, :, 0, :], exact, atol=EXACT_ATOL, rtol=EXACT_RTOL)
     ref = O.fused_attention_compressed(N(qt)[0, :, 0, :], gc_np, 1024, O.default_inv_freq(), stream=stream)
-    assert tol_ok(N(out)[0, :, 0, :], ref)
+    ratio = np.abs(N(out)[0, :, 0, :].astype(np.float64) - ref) / (2e-3 + 1e-2 * np.abs(ref))
+    assert np.mean(ratio <= 1.0) >= 0.999 and ratio.max() <= 1.5, ratio.max()
     # int4 codes of the product == oracle's double quantisation of the product's own projection
     flat = ops.undo_rope(k.to(DEV)[0, :, 4:960, :], 4, inv.to(DEV))
     w = (gc["k_basis_q"].float() * gc["k_basis_scale"].float()).contiguous()
@@ -503,6 +611,47 @@ def test_cache_compress_and_decode_end_to_end(ops):
     # non-fused read path returns full-length fp16 K/V
     cache._fused_decode_update = False
     assert layer.keys.shape == (1, 8, 1025, 128) and layer.values.shape == (1, 8, 1025, 128)
+
+
+def test_pca_fit_quality_against_the_reference_method(ops):
+    """The GPU PCA fit (covariance + symmetric eigensolver) against the reference's randomised
+    `svd_lowrank(niter=24)` on the configs[0] keys.  The basis is an input of the bit-level parity
+    contract, so this comparison is quality-level: at least the captured variance, the same bit
+    allocation, and attention no further from uncompressed fp16 attention."""
+    from shard_b200 import Cache, fused_attention_compressed
+    from shard_b200.cache import pca_fit
+    from shard_b200.rope import dp_bit_allocation
+    import synth
+    k, v, q = synth.make_kvq(2048, 0)
+    inv = synth.rope_inv_freq()
+    flat = ops.undo_rope(k.to(DEV)[0, :, 4:1984, :], 4, inv.to(DEV))
+    mean = flat.mean(dim=0)
+    torch.manual_seed(42)
+    _, S, V = torch.svd_lowrank(flat - mean, q=192, niter=24)
+    basis, eig = pca_fit(flat, mean, 192)
+    xc = flat - mean
+    total = xc.pow(2).sum()
+    var_ref, var_new = ((xc @ V).pow(2).sum() / total).item(), ((xc @ basis).pow(2).sum() / total).item()
+    assert var_new >= var_ref - 1e-6, (var_new, var_ref)
+    eig_ref = (S.float() ** 2) / flat.shape[0]
+    assert torch.allclose(eig, eig_ref, rtol=2e-3, atol=1e-5)
+    budget = max(64, int(1024 * 16 / 20.0))
+    assert dp_bit_allocation(eig, budget) == dp_bit_allocation(eig_ref, budget)
+    assert torch.allclose(basis.T @ basis, torch.eye(192, device=DEV), atol=1e-4)
+    # end to end: compress with either fit, attend, compare with uncompressed attention
+    kk = k.float()[0].repeat_interleave(4, 0)
+    vv = v.float()[0].repeat_interleave(4, 0)
+    sc = torch.einsum("hd,hnd->hn", q.float()[0, :, 0], kk) / 128 ** 0.5
+    full = torch.einsum("hn,hnd->hd", torch.softmax(sc, -1), vv)
+    errs = {}
+    for mode in ("svd_lowrank", "eigh"):
+        cache = Cache(num_layers=1, rope_inv_freq=inv)
+        cache._k_pca = mode
+        cache.layers[0].update(k.to(DEV), v.to(DEV))
+        cache.compress()
+        out = fused_attention_compressed(q.to(DEV), cache.layers[0], 2048, inv, None)
+        errs[mode] = (out.float().cpu()[0, :, 0] - full).abs().max().item()
+    assert errs["eigh"] <= errs["svd_lowrank"] * 1.05 + 1e-3, errs
 
 
 def test_cache_accounting_matches_reference_numbers(golden_chain512):
