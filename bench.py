@@ -820,6 +820,96 @@ def run_seqsplit(args):
         raise SystemExit("sequence-split parity check failed")
 
 
+def run_compress_profile(args):
+    """Prefill compressor, one layer of a T-token sequence: CUDA-event time of every kernel family run
+    on its own (median of 7 after 3 warm-ups), with its algorithmic bytes / FLOPs against the measured
+    peaks, and the whole `Cache.compress()` of the layer.  One GPU."""
+    import torch
+    import synth
+    from shard_b200 import Cache, ops
+    from shard_b200.cache import kmeans, pca_fit
+    from shard_b200.streaming import get_codebook, stream_signs
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    T = args.ctx
+    n = T - SINK - WIN
+    hbm_peak, tf_burst, tf_sustained, peak_kind = measured_peaks()
+    k, v, _ = synth.make_kvq(T, 100, device=dev)
+    inv = synth.rope_inv_freq().to(dev)
+
+    def timed(fn, reps=7, warm=3):
+        for _ in range(warm):
+            fn()
+        ts = []
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    k_mid, v_mid = k[0, :, SINK:T - WIN, :], v[0, :, SINK:T - WIN, :]
+    rows = []
+
+    def row(name, ms, nbytes=None, flops=None, note=""):
+        r = {"kernel": name, "ms": ms, "note": note}
+        if nbytes:
+            r.update(algorithmic_bytes=nbytes, gbs=nbytes / ms / 1e6, hbm_frac=nbytes / ms / 1e6 / hbm_peak)
+        if flops:
+            r.update(algorithmic_flops=flops, tflops=flops / ms / 1e9)
+        rows.append(r)
+
+    flat = ops.undo_rope(k_mid, SINK, inv)
+    row("undo_rope_kernel", timed(lambda: ops.undo_rope(k_mid, SINK, inv)), nbytes=n * 1024 * (2 + 4),
+        note="reads fp16 keys, writes fp32")
+    mean = flat.mean(dim=0).contiguous()
+    basis, eig = pca_fit(flat, mean, RANK)
+    row("pca_fit (torch: Gram matrix GEMM + eigh)", timed(lambda: pca_fit(flat, mean, RANK), reps=3, warm=1),
+        flops=2 * n * 1024 * 1024, note="library GEMM + cuSOLVER eigensolver on 1024 x 1024")
+    scale = basis.abs().amax(0).clamp(min=1e-6) / 127.0
+    w = ((basis / scale).round().clamp(-127, 127) * scale).contiguous()
+    proj = ops.k_project(flat, mean, w)
+    ms = timed(lambda: ops.k_project(flat, mean, w))
+    row("k_project_tc_kernel (+ weight split)", ms, nbytes=n * 1024 * 4 + n * RANK * 4, flops=2 * n * 1024 * RANK,
+        note="3 tf32 MMAs per k-step: tensor work is 3x the algorithmic FLOPs; frac_of_tf32_peak uses half the bf16 peak")
+    rows[-1]["tensor_frac_of_tf32_peak"] = 3 * 2 * n * 1024 * RANK / ms / 1e9 / (tf_burst / 2)
+    alloc = [4] * RANK
+    row("kq_* (min/max, max-abs, scale, pack)", timed(lambda: ops.k_quantize_pack(proj, alloc)),
+        nbytes=3 * n * RANK * 4 + n * RANK // 2, note="three passes over the fp32 projection, writes packed int4")
+    x, ch = ops.v_hadamard_normalise(v_mid)
+    row("v_rotate / v_clamp / v_normalise", timed(lambda: ops.v_hadamard_normalise(v_mid)),
+        nbytes=n * 1024 * (2 + 4 + 4 + 4), note="reads fp16 values, writes fp32, normalises in place")
+    flat_v = x.view(-1, 4)
+    g = torch.Generator(device=dev).manual_seed(42)
+    cent = flat_v[torch.randperm(flat_v.shape[0], generator=g, device=dev)[:256]].clone()
+    sums, counts = torch.zeros_like(cent), torch.zeros(256, device=dev)
+    nsub = flat_v.shape[0]
+    ms = timed(lambda: ops.vq_assign_accumulate(flat_v, cent, sums, counts))
+    row("vq_assign_kernel<true> (one k-means pass)", ms, nbytes=nsub * 17, flops=12 * 256 * nsub,
+        note="fp32 CUDA cores: 256 distances of 4 subtractions, 4 multiply-adds ... per sub-vector")
+    row("kmeans (30 iterations at most)", timed(lambda: kmeans(flat_v, 256, n_iter=30), reps=3, warm=1), note="whole V codebook fit")
+    cb, signs = get_codebook(HD, 8, dev), stream_signs(0, HD, dev)
+    bufs = [torch.zeros(16, N_KV, HD, dtype=torch.uint8, device=dev) for _ in range(2)] + \
+           [torch.zeros(16, N_KV, dtype=torch.float16, device=dev) for _ in range(2)]
+    tk, tv = k[0, :, 0, :].contiguous(), v[0, :, 0, :].contiguous()
+    row("stream_quantize_kernel", timed(lambda: ops.stream_quantize(tk, tv, signs, cb, *bufs, 0)), nbytes=2 * N_KV * HD * 3,
+        note="one token: launch latency")
+    cache = Cache(num_layers=1, rope_inv_freq=synth.rope_inv_freq())
+    cache.layers[0].update(k, v)
+    cache.compress()
+    line = {"metric": "prefill_compress_s_per_layer", "value": cache.compress_seconds, "unit": "s", "n_gpus": 1,
+            "steps": 1, "warmup": 0, "ms_per_step": cache.compress_seconds * 1e3, "higher_is_better": False,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"prefill compression of one layer, {T}-token sequence (n_comp = {n}), Llama-3.1-8B geometry"},
+            "peaks": {"hbm_gbs": hbm_peak, "bf16_tflops_burst": tf_burst, "kind": peak_kind}, "kernels": rows,
+            "e2e": {"value": None, "unit": "s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": len(rows)}
+    print(json.dumps(line), flush=True)
+
+
 def run_generate(args):
     """BASELINE configs[1]: a random-init Llama-3.1-8B-shape decoder driven through HF `generate`
     semantics -- prefill 8192 synthetic ids, compress the cache, decode greedily with the 8-bit
@@ -910,11 +1000,12 @@ def main():
     ap.add_argument("--ctx", type=int, default=32768)
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--seqs", type=int, default=1, help="sequences per GPU (cfg2)")
-    ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4"],
+    ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "compress"],
                     help="cfg1: Llama-8B-shape decoder, 8K prefill + greedy decode through the HF hook (1 GPU); "
                          "cfg2: one 32K sequence per GPU (headline; at N > 1 the line also carries cfg4 and cfg3 "
                          "records); cfg3: 64 x 8K sequences sharded by batch; "
-                         "cfg4: one 131072-token sequence split by token range")
+                         "cfg4: one 131072-token sequence split by token range; "
+                         "compress: per-kernel timing of the prefill compressor on one layer (1 GPU)")
     ap.add_argument("--merge", default="peer", choices=["peer", "nccl", "both"],
                     help="cfg4 at N > 1: deliver the partial records over peer memory from inside the decode "
                          "launch (default), or NCCL all-gather followed by a merge launch, or time both")
@@ -933,6 +1024,8 @@ def main():
         run_batch64(args)
     elif args.workload == "cfg1":
         run_generate(args)
+    elif args.workload == "compress":
+        run_compress_profile(args)
     else:
         run_ours(args)
 

@@ -51,7 +51,9 @@ constexpr int PP_TMEM_COLS = 512;
 constexpr int PP_COL_A = 256;
 constexpr int PP_COL_SO = 360;
 constexpr float PP_LAZY_LOG2 = 8.f;   // a softmax reference point moves only when exceeded by more than 2^8
-constexpr int PP_V_BYTES = 32768, PP_P_BYTES = 4096, PP_Q_BYTES = 4096, PP_CB_BYTES = 2048;
+constexpr int PP_V_BYTES = 32768, PP_P_BYTES = 4096, PP_Q_BYTES = 4096;
+constexpr int PP_CB_COPIES = 4;       // interleaved copies of the V codebook: lane l reads copy l % 4, entry e of copy c at 4e + c
+constexpr int PP_CB_BYTES = 2048 * PP_CB_COPIES;
 constexpr int PP_ROWQ_BYTES = (GQA * HD + 256) * 4;   // queries as given + stream codebook, for the row path
 constexpr int PP_MISC_BYTES = 1024 + 1024;   // state + barriers, and slack for 1 KB alignment
 
@@ -227,7 +229,11 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     *abort_s = 0;
     fence_mbar_init();
   }
-  if (tid >= 256) cbv[tid - 256] = reinterpret_cast<const uint2*>(sq.v_centroids)[tid - 256];
+  if (tid >= 256) {
+    const uint2 e = reinterpret_cast<const uint2*>(sq.v_centroids)[tid - 256];
+#pragma unroll
+    for (int c = 0; c < PP_CB_COPIES; ++c) cbv[PP_CB_COPIES * (tid - 256) + c] = e;
+  }
   else if (tid >= 32 && tid < 128 && sh.n_stream > 0)
     for (int i = tid - 32; i < 256; i += 96) cbs_s[i] = p.codebook[i];
   {
@@ -339,6 +345,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     // gather work of the three non-issuing warps: 512 units of (token row, 8 codes), 96 threads
     const int gq = quad - (quad > issuer_quad ? 1 : 0);        // 0..2 among the gathering warps
     const int gather_first = gq * 32 + lane;
+    const uint2* cbv4 = cbv + (lane & (PP_CB_COPIES - 1));   // this lane's copy of the codebook (fewer bank conflicts)
 
     bool bad = false;
     if (issuer && g < 2 && g < n_my) bad |= !issue_mma1(g);
@@ -415,16 +422,20 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       if (use > 0) bad |= !mbar_wait(O_DONE(g), (uint32_t)((use - 1) & 1), abort_s);
       bad |= !mbar_wait(V_FULL(g), par, abort_s);
       if (quad != issuer_quad) {
-#pragma unroll 2
-        for (int u = gather_first; u < 512; u += 96) {
-          const int row = u >> 2, part = u & 3;               // codes 8*part .. 8*part+7 of the row
-          const uint2 cw = *reinterpret_cast<const uint2*>(vc_g + row * VQ_GROUPS + 8 * part);
+        // 256 units of (token row, 16 codes) over 96 threads; consecutive lanes take consecutive rows,
+        // so the eight 16-byte stores of a quarter-warp fall into eight different bank groups of the
+        // swizzled tile
+#pragma unroll 1
+        for (int u = gather_first; u < 256; u += 96) {
+          const int row = u & 127, hf = u >> 7;              // codes 16*hf .. 16*hf+15 of the row
+          const uint4 cq = *reinterpret_cast<const uint4*>(vc_g + row * VQ_GROUPS + 16 * hf);
+          const uint32_t cw[4] = {cq.x, cq.y, cq.z, cq.w};
+          unsigned char* dst = v_g + hf * 16384;
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            const uint32_t two = (jj < 2 ? cw.x : cw.y) >> (16 * (jj & 1));
-            const uint2 e0 = cbv[two & 0xff], e1 = cbv[(two >> 8) & 0xff];
-            const int j = 4 * part + jj;                      // 8-channel chunk of the row
-            *reinterpret_cast<uint4*>(v_g + (j >> 3) * 16384 + sw128_off(row, j & 7)) = make_uint4(e0.x, e0.y, e1.x, e1.y);
+          for (int jj = 0; jj < 8; ++jj) {
+            const uint32_t two = cw[jj >> 1] >> (16 * (jj & 1));
+            const uint2 e0 = cbv4[4 * (two & 0xff)], e1 = cbv4[4 * ((two >> 8) & 0xff)];
+            *reinterpret_cast<uint4*>(dst + sw128_off(row, jj)) = make_uint4(e0.x, e0.y, e1.x, e1.y);
           }
         }
       }
