@@ -540,9 +540,11 @@ def measure_seqsplit(D, L, K, W, T=131072, merge="peer", with_n1=True):
                 layer.update(k_pool[j, li], v_pool[j, li])           # stream append (rank 0 owns the stream)
             e = ev[(j - W) * L + li] if events else None
             if e: e[0].record()
-            if use_peer:
+            if use_peer and not events:
+                peer.decode_merge(q_pool[j, li], layer, pos, out[li], with_fp16_segments=first)   # one launch
+            elif use_peer:
                 decode_layer(q_pool[j, li], layer, pos, partial_out=True, with_fp16_segments=first, push=peer)
-                if e: e[1].record()
+                e[1].record()
                 peer.wait_merge(out[li])
             else:
                 decode_layer(q_pool[j, li], layer, pos, partial_out=True, with_fp16_segments=first, out=part)
@@ -588,7 +590,9 @@ def measure_seqsplit(D, L, K, W, T=131072, merge="peer", with_n1=True):
                           "merge_us_per_layer": mrg_ms * 1e3 / L,
                           "note": "pass with CUDA events around every launch (no launch overlap)"},
                decode_us_per_layer=dec_ms * 1e3 / L, merge_us_per_layer=mrg_ms * 1e3 / L,
-               merge="decode launch delivers over NVLink peer memory + polling merge kernel" if peer is not None
+               merge="one launch per rank: the decode launch delivers its record over NVLink peer memory, waits for "
+                     "the others' and merges (the breakdown pass uses a second, polling launch for the merge)"
+               if peer is not None
                else ("NCCL all-gather + merge launch" if D.world > 1 else "single GPU: merge launch only"))
     if D.world > 1 and merge == "both":
         # the NCCL path beside it (the stream keeps growing meanwhile: well under 1 us per layer on rank 0)

@@ -239,12 +239,15 @@ int shard_b200_lse_merge(const float* parts, int32_t n_parts, int32_t n_q, void*
  * `world` device pointers (entry `rank` = own buffer); `epoch` starts at 1 and grows by 1 per
  * call, in step on all ranks.
  *
- * Faster form of the same step: shard_b200_decode_attn_seqsplit is shard_b200_decode_attn for one
+ * Faster forms of the same step: shard_b200_decode_attn_seqsplit is shard_b200_decode_attn for one
  * sequence (shape.partial_out must be 1) whose combining CTAs deliver the record straight into
- * every rank's buffer and publish `epoch` -- the decode launch does the exchange -- and
- * shard_b200_seqsplit_wait_merge is the wait + merge half alone, launched so that it is already
- * polling while the decode launch in front of it runs.  seq_host->out may be NULL there.  Per
- * epoch a rank uses either shard_b200_seqsplit_merge or this pair; ranks may differ.
+ * every rank's buffer and publish `epoch` -- the decode launch does the exchange.  With
+ * merged_out_f16 set (fp16 [4*nkv][128]) the same CTAs then wait, bounded by `timeout_us` like
+ * above (status_dev), for all ranks' records and write the merged attention output: the whole
+ * step is ONE launch per rank.  With merged_out_f16 == NULL the wait + merge half is a launch of
+ * its own, shard_b200_seqsplit_wait_merge, started so that it is already polling while the decode
+ * launch in front of it runs.  seq_host->out may be NULL in both.  Per epoch a rank uses one of the
+ * three forms; ranks may differ.
  */
 size_t shard_b200_peer_buffer_bytes(int32_t world, int32_t nkv);
 int shard_b200_peer_alloc(size_t bytes, void** ptr_out, void* handle_out_64);
@@ -257,7 +260,8 @@ int shard_b200_seqsplit_merge(const float* my_part, void* const* bufs_host, int3
 int shard_b200_decode_attn_seqsplit(const ShardSeq* seq_host, const ShardDecodeShape* shape_host,
                                     const float* inv_freq, const float* codebook, void* workspace,
                                     size_t workspace_bytes, void* const* bufs_host, int32_t rank,
-                                    int32_t world, uint32_t epoch, void* stream);
+                                    int32_t world, uint32_t epoch, void* merged_out_f16, int* status_dev,
+                                    uint32_t timeout_us, void* stream);
 int shard_b200_seqsplit_wait_merge(void* const* bufs_host, int32_t rank, int32_t world, int32_t nkv,
                                    uint32_t epoch, void* out_f16, int* status_dev, uint32_t timeout_us,
                                    void* stream);

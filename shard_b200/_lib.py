@@ -57,7 +57,7 @@ _SIGNATURES = {
                                             C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "shard_b200_decode_attn_seqsplit": (C.c_int, [C.c_void_p, C.POINTER(ShardDecodeShape), C.c_void_p, C.c_void_p,
                                                   C.c_void_p, C.c_size_t, C.c_void_p, C.c_int32, C.c_int32,
-                                                  C.c_uint32, C.c_void_p]),
+                                                  C.c_uint32, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "shard_b200_seqsplit_wait_merge": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_uint32,
                                                  C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "shard_b200_decode_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p]),

@@ -279,7 +279,8 @@ extern "C" int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const
 extern "C" int shard_b200_decode_attn_seqsplit(const ShardSeq* seq_host, const ShardDecodeShape* shape_host,
                                                const float* inv_freq, const float* codebook, void* workspace,
                                                size_t workspace_bytes, void* const* bufs_host, int32_t rank,
-                                               int32_t world, uint32_t epoch, void* stream) {
+                                               int32_t world, uint32_t epoch, void* merged_out_f16,
+                                               int* status_dev, uint32_t timeout_us, void* stream) {
   if (!bufs_host || world < 1 || world > PEER_MAX_WORLD || rank < 0 || rank >= world || epoch == 0 || !shape_host)
     return SHARD_E_ARG;
   if (!shape_host->partial_out) return SHARD_E_ARG;   // what travels is the unnormalised record
@@ -291,6 +292,9 @@ extern "C" int shard_b200_decode_attn_seqsplit(const ShardSeq* seq_host, const S
   push.rank = rank;
   push.world = world;
   push.epoch = epoch;
+  push.merged_out = merged_out_f16;
+  push.status = status_dev;
+  push.wait_ns = timeout_us ? (unsigned long long)timeout_us * 1000ull : PEER_DEFAULT_WAIT_NS;
   return decode_attn_impl(seq_host, 1, shape_host, inv_freq, codebook, workspace, workspace_bytes, &push, stream);
 }
 

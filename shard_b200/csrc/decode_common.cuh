@@ -17,6 +17,9 @@ struct PeerPush {
   unsigned char* bufs[PEER_MAX_WORLD];
   int rank, world;
   unsigned int epoch;
+  void* merged_out;              // fp16 [n_q][128]: if set, the delivering CTA also waits for all ranks' records and merges
+  int* status;                   // set to 1 when that wait gives up (may be null)
+  unsigned long long wait_ns;    // its bound
 };
 
 struct DecodeParams {
@@ -306,6 +309,26 @@ __device__ __forceinline__ void ticket_combine(const DecodeParams& p, const Shar
       volatile unsigned int* flag = reinterpret_cast<volatile unsigned int*>(p.push.bufs[tid]) +
                                     ((size_t)slot * p.push.world + p.push.rank) * p.sh.nkv + kv;
       *flag = p.push.epoch;
+    }
+    if (p.push.merged_out) {
+      // ... and finishes the step itself: wait -- bounded by the global timer -- for every rank's
+      // records of this KV head in the own buffer, merge them in rank order, write the attention
+      // output.  (Eight CTAs of the launch do this, one per KV head, while the others have retired.)
+      if (tid == 0) last_s = 0;                        // reused as "gave up"
+      __syncthreads();
+      if (tid < p.push.world) {
+        volatile unsigned int* flag = reinterpret_cast<volatile unsigned int*>(p.push.bufs[p.push.rank]) +
+                                      ((size_t)slot * p.push.world + tid) * p.sh.nkv + kv;
+        if (!wait_epoch(flag, p.push.epoch, p.push.wait_ns)) last_s = 1;
+        __threadfence_system();
+      }
+      __syncthreads();
+      if (last_s) {
+        if (tid == 0 && p.push.status) atomicExch(p.push.status, 1);
+      } else if (active) {
+        reinterpret_cast<__half*>(p.push.merged_out)[(size_t)h * HD + d] =
+            merge_rank_records(p.push.bufs[p.push.rank], p.push.world, p.sh.nkv, slot, h, d);
+      }
     }
     if (!sq.out) return;
   }

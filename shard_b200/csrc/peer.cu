@@ -25,29 +25,6 @@
 
 namespace shard {
 
-constexpr unsigned long long PEER_DEFAULT_WAIT_NS = 200ull * 1000 * 1000;   // 0.2 s
-
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
-// Waits until *flag == epoch or `limit_ns` nanoseconds have passed; false on time-out.
-__device__ __forceinline__ bool wait_epoch(volatile unsigned int* flag, unsigned int epoch,
-                                           unsigned long long limit_ns) {
-  if (*flag == epoch) return true;
-  const unsigned long long t0 = global_timer_ns();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i) {
-      if (*flag == epoch) return true;
-      __nanosleep(32);
-    }
-    if (global_timer_ns() - t0 > limit_ns) return false;
-  }
-}
-
 struct PeerParams {
   unsigned char* bufs[PEER_MAX_WORLD];   // exchange buffer of every rank (own entry = local pointer)
   const float* my_part;                  // [n_q][132]
@@ -60,23 +37,8 @@ struct PeerParams {
 
 // (4): merge of the `world` records of KV head kv in the own buffer, in rank order
 __device__ __forceinline__ void merge_own_buffer(const PeerParams& p, int kv, int tid, int slot) {
-  const int n_q = p.nkv * GQA;
-  const size_t flag_bytes = peer_flag_bytes(p.world, p.nkv);
-  const size_t slot_floats = peer_slot_floats(p.world, p.nkv);
   const int h = kv * GQA + (tid >> 7), d = tid & (HD - 1);
-  const float* base = reinterpret_cast<const float*>(p.bufs[p.rank] + flag_bytes) + slot * slot_floats + (size_t)h * PART;
-  const size_t pstride = (size_t)n_q * PART;
-  float M = neg_inf();
-  for (int r = 0; r < p.world; ++r) M = fmaxf(M, __ldcg(base + r * pstride));
-  float L = 0.f, acc = 0.f;
-  for (int r = 0; r < p.world; ++r) {
-    const float* rec = base + r * pstride;
-    const float m = __ldcg(rec);
-    const float wt = (m == neg_inf()) ? 0.f : exp2f((m - M) * LOG2E);
-    L = fmaf(wt, __ldcg(rec + 1), L);
-    acc = fmaf(wt, __ldcg(rec + 4 + d), acc);
-  }
-  reinterpret_cast<__half*>(p.out)[(size_t)h * HD + d] = __float2half_rn(acc / L);
+  reinterpret_cast<__half*>(p.out)[(size_t)h * HD + d] = merge_rank_records(p.bufs[p.rank], p.world, p.nkv, slot, h, d);
 }
 
 __global__ void __launch_bounds__(GQA* HD) seqsplit_exchange_merge_kernel(const __grid_constant__ PeerParams p) {

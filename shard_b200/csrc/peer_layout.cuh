@@ -19,4 +19,50 @@ __host__ __device__ inline size_t peer_flag_bytes(int world, int nkv) {
 }
 __host__ __device__ inline size_t peer_slot_floats(int world, int nkv) { return (size_t)world * nkv * GQA * PART; }
 
+constexpr unsigned long long PEER_DEFAULT_WAIT_NS = 200ull * 1000 * 1000;   // 0.2 s
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Waits until *flag == epoch or `limit_ns` nanoseconds of the GPU's global timer have passed;
+// false on time-out.
+__device__ __forceinline__ bool wait_epoch(volatile unsigned int* flag, unsigned int epoch,
+                                           unsigned long long limit_ns) {
+  if (*flag == epoch) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (*flag == epoch) return true;
+      __nanosleep(32);
+    }
+    if (global_timer_ns() - t0 > limit_ns) return false;
+  }
+}
+
+// Merge of the `world` records of query head h, channel d, in slot `slot` of this rank's own
+// exchange buffer, in rank order: the operations and order of decode_combine_kernel, so every
+// rank computes bit-identical output.
+__device__ __forceinline__ __half merge_rank_records(const unsigned char* own_buf, int world, int nkv, int slot,
+                                                     int h, int d) {
+  const int n_q = nkv * GQA;
+  const float* base = reinterpret_cast<const float*>(own_buf + peer_flag_bytes(world, nkv)) +
+                      slot * peer_slot_floats(world, nkv) + (size_t)h * PART;
+  const size_t pstride = (size_t)n_q * PART;
+  float M = neg_inf();
+  for (int r = 0; r < world; ++r) M = fmaxf(M, __ldcg(base + r * pstride));
+  float L = 0.f, acc = 0.f;
+  for (int r = 0; r < world; ++r) {
+    const float* rec = base + r * pstride;
+    const float m = __ldcg(rec);
+    const float wt = (m == neg_inf()) ? 0.f : exp2f((m - M) * LOG2E);
+    L = fmaf(wt, __ldcg(rec + 1), L);
+    acc = fmaf(wt, __ldcg(rec + 4 + d), acc);
+  }
+  return __float2half_rn(acc / L);
+}
+
 }  // namespace shard

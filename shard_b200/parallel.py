@@ -129,6 +129,7 @@ class PeerExchange:
         self._ptrs = (C.c_void_p * self.world)(*ptrs)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.epoch = 0
+        self.fused_out = None
         dist.barrier(group=group)            # every buffer is zeroed and opened before the first store
 
     def merge(self, part: torch.Tensor, out: torch.Tensor | None = None):
@@ -145,11 +146,32 @@ class PeerExchange:
     # -- fused form: the decode launch delivers, a polling kernel merges -----------------------
     def launch_decode(self, seq, shape, inv_ptr, cb_ptr, ws):
         """Called by `decode_layer(..., push=self)`: the decode launch of the NEXT epoch, whose
-        combining CTAs store the rank's record into every rank's buffer and publish the epoch."""
+        combining CTAs store the rank's record into every rank's buffer and publish the epoch.
+        With `self.fused_out` set (by `decode_merge`) the same CTAs also wait for all ranks' records
+        and write the merged output there: the step is one launch."""
         import ctypes as C
+        fused = self.fused_out
         _lib.check(_lib.load().shard_b200_decode_attn_seqsplit(
             C.addressof(seq), C.byref(shape), inv_ptr, cb_ptr, ws.data_ptr(), ws.numel() * ws.element_size(),
-            self._ptrs, self.rank, self.world, self.epoch + 1, _lib.cur_stream()), "decode_attn_seqsplit")
+            self._ptrs, self.rank, self.world, self.epoch + 1,
+            None if fused is None else fused.data_ptr(), self.status.data_ptr(), self.timeout_us,
+            _lib.cur_stream()), "decode_attn_seqsplit")
+        if fused is not None:
+            self.epoch += 1
+
+    def decode_merge(self, q_rope, layer, pos_q, out: torch.Tensor | None = None, with_fp16_segments=True):
+        """One launch: decode this rank's slice, deliver the record to every rank, wait for theirs,
+        merge.  Returns the (n_q, 128) fp16 output (identical on all ranks)."""
+        from .attention import decode_layer
+        n_q = 4 * self.nkv
+        if out is None:
+            out = torch.empty(n_q, 128, dtype=torch.float16, device=self.dev)
+        self.fused_out = out
+        try:
+            decode_layer(q_rope, layer, pos_q, partial_out=True, with_fp16_segments=with_fp16_segments, push=self)
+        finally:
+            self.fused_out = None
+        return out
 
     def wait_merge(self, out: torch.Tensor | None = None):
         """Wait for every rank's record of the epoch `launch_decode` delivered and merge them."""
@@ -213,10 +235,12 @@ def seqsplit_decode(q_rope, layer, pos_q, group=None, gather_buf=None, timing=No
     idle = gc["n_compress"] == 0 and n_rows == 0
     out2 = None if out is None else out.view(n_q, q_rope.shape[3])
     if peer is not None and not idle:
-        decode_layer(q_rope, layer, pos_q, partial_out=True, with_fp16_segments=first, out=part_buf, push=peer)
-        if timing is not None:
+        if timing is None:
+            res = peer.decode_merge(q_rope, layer, pos_q, out2, with_fp16_segments=first)   # one launch
+        else:
+            decode_layer(q_rope, layer, pos_q, partial_out=True, with_fp16_segments=first, out=part_buf, push=peer)
             timing["merge_start"].record()
-        res = peer.wait_merge(out2)
+            res = peer.wait_merge(out2)
     else:
         part = (neutral_partial(n_q, q_rope.device) if idle else
                 decode_layer(q_rope, layer, pos_q, partial_out=True, with_fp16_segments=first, out=part_buf))

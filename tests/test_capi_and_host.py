@@ -68,7 +68,7 @@ def test_argument_validation_without_gpu():
     sh1 = ops.make_shape(32, 8, 192, 1000, 0, 1000, 4, 64, 0, 1068, partial_out=False)
     bufs = (C.c_void_p * 2)(1, 1)
     assert lib.shard_b200_decode_attn_seqsplit(C.addressof(seq), C.byref(sh1), None, None, None, 0, bufs, 0, 2, 1,
-                                               None) == -1       # the record that travels is the partial one
+                                               None, None, 0, None) == -1   # the record that travels is the partial one
     assert lib.shard_b200_decode_status(None, None, None) == -1
     assert lib.shard_b200_vq_assign_accumulate(None, None, 10, None, None, None, None) == -1
     assert lib.shard_b200_phase_table_bytes(33) == 64 * 256

@@ -47,8 +47,11 @@ assert all(x == gathered[0] for x in gathered)      # bitwise identical on every
 # the same exchange over NVLink peer memory inside the merge kernel: bit-identical to the NCCL path,
 # also when the two buffer slots are reused over several steps
 peer = PeerExchange(8)
-for step in range(5):
-    out2 = seqsplit_decode(q, mine, 5100, peer=peer)
+for step in range(6):
+    # odd steps: one launch per rank (the delivering CTAs wait and merge); even steps: the decode
+    # launch delivers and a second, already polling launch merges
+    timing = None if step % 2 else {"merge_start": torch.cuda.Event(), "merge_end": torch.cuda.Event()}
+    out2 = seqsplit_decode(q, mine, 5100, peer=peer, timing=timing)
     torch.cuda.synchronize()
     peer.check()
     assert out2.cpu().numpy()[0, :, 0, :].tobytes() == got.tobytes(), step

@@ -29,9 +29,13 @@ class _LocalRank:
 
     def launch_decode(self, seq, shape, inv_ptr, cb_ptr, ws):
         from shard_b200 import _lib
+        fused = getattr(self, "fused_out", None)
         _lib.check(_lib.load().shard_b200_decode_attn_seqsplit(
             C.addressof(seq), C.byref(shape), inv_ptr, cb_ptr, ws.data_ptr(), ws.numel(), self._ptrs, self.rank,
-            self.world, self.epoch + 1, _lib.cur_stream()), "decode_attn_seqsplit")
+            self.world, self.epoch + 1, None if fused is None else fused.data_ptr(), self.status.data_ptr(), 50000,
+            _lib.cur_stream()), "decode_attn_seqsplit")
+        if fused is not None:
+            self.epoch += 1
 
     def wait_merge(self, out, timeout_us=0):
         from shard_b200 import _lib
@@ -108,6 +112,38 @@ def test_decode_launch_delivers_and_polling_kernel_merges(world):
         torch.cuda.synchronize()
         assert all(np.array_equal(a.cpu().numpy(), got[0]) for a in alt)
         status2.zero_()          # the first pass of ranks 0 .. world-2 ran out of time by design
+
+
+def test_one_launch_step_with_a_world_of_one_and_its_wait_running_out():
+    """The one-launch form (the delivering CTAs also wait and merge): with a world of one it must
+    reproduce the plain decode bit for bit; with a world of two whose other rank never delivers, its
+    bounded wait gives up, reports through the status word and leaves the output alone."""
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    from gpu_helpers import FakeCache, FakeLayer, gc_to_device, random_gc, random_query
+    from shard_b200.attention import decode_layer
+    gc_np = random_gc(2000, seed=81)
+    layer = FakeLayer(gc_to_device(gc_np), FakeCache(torch.from_numpy(O.default_inv_freq())))
+    q = torch.from_numpy(random_query(seed=82)).to(DEV).view(1, 32, 1, 128)
+    plain = decode_layer(q, layer, 2100).cpu().numpy()
+    bufs, ptrs = _exchange_buffers(1)
+    rk = _LocalRank(ptrs, 0, 1)
+    for step in range(3):                                # both slots, reused
+        rk.fused_out = torch.full((32, 128), float("nan"), dtype=torch.float16, device=DEV)
+        decode_layer(q, layer, 2100, partial_out=True, push=rk)
+        torch.cuda.synchronize()
+        assert int(rk.status.item()) == 0
+        assert np.array_equal(rk.fused_out.cpu().numpy(), plain)
+    bufs2, ptrs2 = _exchange_buffers(2)
+    lone = _LocalRank(ptrs2, 0, 2)
+    lone.fused_out = torch.full((32, 128), 7.0, dtype=torch.float16, device=DEV)
+    t0 = time.perf_counter()
+    decode_layer(q, layer, 2100, partial_out=True, push=lone)   # rank 1 never delivers: 50 ms bound
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert 0.045 <= waited < 0.6, waited
+    assert int(lone.status.item()) == 1 and bool((lone.fused_out == 7.0).all())
+    assert np.array_equal(decode_layer(q, layer, 2100).cpu().numpy(), plain)   # the context is fine
 
 
 @pytest.mark.parametrize("kernel", ["exchange_merge", "wait_merge"])
