@@ -249,32 +249,85 @@ __device__ __forceinline__ void ticket_combine(const DecodeParams& p, const Shar
   const int hl = (tid >> 7) & (GQA - 1), h = kv * GQA + hl, d = tid & (HD - 1);
   const float* base0 = p.ws + ((size_t)b * n_parts * n_q + (size_t)kv * GQA) * PART;
   const size_t pstride = (size_t)n_q * PART;
-  // (max, sum-exp) of every part of the four heads: one load per thread, all in flight together
-  volatile float* ms = sm + GQA * HD;                 // [GQA][n_parts]
-  volatile float* ls = ms + GQA * n_parts;            // [GQA][n_parts]
-  for (int idx = tid; idx < GQA * n_parts; idx += NTHREADS) {
-    const int hh = idx / n_parts, pi = idx - hh * n_parts;
-    const float* rec = base0 + pi * pstride + hh * PART;
-    ms[idx] = __ldcg(rec);
-    ls[idx] = __ldcg(rec + 1);
-  }
-  __syncthreads();
+  // This CTA is on the critical path of the launch: nobody else is left.
   float M = neg_inf(), L = 0.f, rot = 0.f, stdv = 0.f;
-  if (active) {
-    for (int pi = 0; pi < n_parts; ++pi) M = fmaxf(M, ms[hl * n_parts + pi]);
-    const float* accp = base0 + hl * PART + 4 + d;
+  const float* accp = base0 + hl * PART + 4 + d;
+  if (n_parts <= 64) {
+    // Every load goes out before anything is waited for, so the merge costs one round trip to L2
+    // and no shared memory: lane j of a warp fetches (max, sum-exp) of parts j and j + 32 of the
+    // warp's head -- the same for all its lanes -- and every thread its channel of every part (a
+    // launch over one sequence of a model with 8 KV heads has 36 parts).
+    constexpr int COMBINE_BATCH = 36;
+    const int lane = tid & 31;
+    float a0[COMBINE_BATCH];
+#pragma unroll
+    for (int pi = 0; pi < COMBINE_BATCH; ++pi) a0[pi] = (active && pi < n_parts) ? __ldcg(accp + pi * pstride) : 0.f;
+    float mj[2], lj[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int pj = lane + 32 * k;
+      const float* rec = base0 + pj * pstride + hl * PART;
+      mj[k] = (active && pj < n_parts) ? __ldcg(rec) : neg_inf();
+      lj[k] = (active && pj < n_parts) ? __ldcg(rec + 1) : 0.f;
+    }
+    if (active) {                                      // whole warps: tid < GQA * HD
+      M = warp_max(fmaxf(mj[0], mj[1]));
+      float wj[2];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) wj[k] = (mj[k] == neg_inf()) ? 0.f : exp2f((mj[k] - M) * LOG2E);
+      // (parts in ascending order, the same operations as decode_combine_kernel)
+#pragma unroll
+      for (int pi = 0; pi < COMBINE_BATCH; ++pi) {
+        const float wt = __shfl_sync(0xffffffffu, wj[pi >> 5], pi & 31);
+        const float lp = __shfl_sync(0xffffffffu, lj[pi >> 5], pi & 31);
+        if (pi < n_parts) {
+          L = fmaf(wt, lp, L);
+          if (pi < n_rot) rot = fmaf(wt, a0[pi], rot); else stdv = fmaf(wt, a0[pi], stdv);
+        }
+      }
+      for (int pi = COMBINE_BATCH; pi < n_parts; ++pi) {
+        const float wt = __shfl_sync(0xffffffffu, wj[pi >> 5], pi & 31);
+        const float lp = __shfl_sync(0xffffffffu, lj[pi >> 5], pi & 31);
+        const float a = __ldcg(accp + pi * pstride);
+        L = fmaf(wt, lp, L);
+        if (pi < n_rot) rot = fmaf(wt, a, rot); else stdv = fmaf(wt, a, stdv);
+      }
+    }
+  } else {
+    // many parts: (max, sum-exp) of every part of the four heads staged in shared memory
+    volatile float* ms = sm + GQA * HD;                 // [GQA][n_parts]
+    volatile float* ls = ms + GQA * n_parts;            // [GQA][n_parts]
+    for (int idx = tid; idx < GQA * n_parts; idx += NTHREADS) {
+      const int hh = idx / n_parts, pi = idx - hh * n_parts;
+      const float* rec = base0 + pi * pstride + hh * PART;
+      ms[idx] = __ldcg(rec);
+      ls[idx] = __ldcg(rec + 1);
+    }
+    __syncthreads();
+    if (active) {
+      for (int pi = 0; pi < n_parts; ++pi) M = fmaxf(M, ms[hl * n_parts + pi]);
 #pragma unroll 12
-    for (int pi = 0; pi < n_parts; ++pi) {
-      const float a = __ldcg(accp + pi * pstride);
-      const float m = ms[hl * n_parts + pi];
-      const float wt = (m == neg_inf()) ? 0.f : exp2f((m - M) * LOG2E);
-      L = fmaf(wt, ls[hl * n_parts + pi], L);
-      if (pi < n_rot) rot = fmaf(wt, a, rot); else stdv = fmaf(wt, a, stdv);
+      for (int pi = 0; pi < n_parts; ++pi) {
+        const float a = __ldcg(accp + pi * pstride);
+        const float m = ms[hl * n_parts + pi];
+        const float wt = (m == neg_inf()) ? 0.f : exp2f((m - M) * LOG2E);
+        L = fmaf(wt, ls[hl * n_parts + pi], L);
+        if (pi < n_rot) rot = fmaf(wt, a, rot); else stdv = fmaf(wt, a, stdv);
+      }
     }
   }
+  // inverse (= forward) normalised Hadamard of the rotated-space sum over the 128 channels of a
+  // head (four warps): the butterflies inside a warp by shuffle, the last two through shared memory
   float v = rot;
   if (n_rot > 0) {
-    for (int hh = 1; hh < HD; hh <<= 1) {
+    if (active) {
+#pragma unroll
+      for (int hh = 1; hh < 32; hh <<= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, v, hh);
+        v = (d & hh) ? other - v : v + other;
+      }
+    }
+    for (int hh = 32; hh < HD; hh <<= 1) {
       if (active) sm[tid] = v;
       __syncthreads();
       if (active) {

@@ -26,9 +26,9 @@
 //                       start-up slack of the last consumer group
 //   combine             the last CTA of a (sequence, KV head) to finish merges all records
 //
-// Stage s of tensor memory: columns [128s, 128s+128): un-rotated keys (fp32), overwritten in
-// place by K~ (fp16x2, columns 0-63 of the stage), scores (64-79) and the tile's P.V (80-95);
-// the A operand sits at [384, 488).
+// Tensor memory: two key stages of 128 columns (tile t uses stage t % 2: un-rotated keys in fp32,
+// overwritten in place by K~ as fp16x2 in columns 0-63 of the stage), the A operand at [256, 360),
+// and per consumer group 16 columns of scores and 16 of P.V accumulator from column 360 on.
 // Every hand-over is an mbarrier whose waiters see each of its phases; every wait is bounded and
 // raises the CTA's abort flag when it gives up, after which all roles drain, bulk copies in flight
 // are waited for, tensor memory is freed and the status word is set.
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   volatile int* abort_s = reinterpret_cast<volatile int*>(misc + 145);
   volatile int* c_cnt = reinterpret_cast<volatile int*>(misc + 146);   // [2] coefficient tiles requested per buffer
   volatile int* mma1_next = reinterpret_cast<volatile int*>(misc + 208);   // next tile whose MMA1 is to be issued
-  uint64_t* bars = reinterpret_cast<uint64_t*>(misc + 148);        // 28 mbarriers
+  uint64_t* bars = reinterpret_cast<uint64_t*>(misc + 148);        // 29 mbarriers
 
   const ShardSeq& sq = p.table ? p.table[blockIdx.z] : p.one;
   const ShardDecodeShape& sh = p.sh;
@@ -175,6 +175,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   auto C_FULL = [&](int b) { return bar0 + 8u * (uint32_t)(19 + b); };    // coefficient tile has landed
   auto V_FULL = [&](int g) { return bar0 + 8u * (uint32_t)(21 + g); };    // V code tile has landed
   const uint32_t APPEND_DONE = bar0 + 8u * 24u;                           // the newest streamed row has been written
+  const uint32_t Q_READY = bar0 + 8u * 28u;                               // the query operand and the fp32 queries are staged
 
   // tiles of this chunk: evenly spread, the first `tiles_rem` chunks get one more
   const int tile_lo = part * p.tiles_per_chunk + min(part, p.tiles_rem);
@@ -226,6 +227,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     *mma1_next = 0;
     for (int j = 0; j < 3; ++j) mbar_init(A_FULL(j), 4);
     mbar_init(APPEND_DONE, 2);
+    mbar_init(Q_READY, 4);
     *abort_s = 0;
     fence_mbar_init();
   }
@@ -240,34 +242,6 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     // P rows that a token's warp does not own stay zero for the whole kernel
     uint4* z = reinterpret_cast<uint4*>(p_s);
     for (int i = tid; i < (PP_STAGES * PP_P_BYTES) / 16; i += PP_THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
-  }
-  // Up to here only tensors that no decode call ever writes were touched (weights, coefficients,
-  // V codes, codebooks).  The query, the new token, the stream rows, the phase table, the scratch
-  // and the output may come from, or still be in use by, the call before this one.
-  griddep_wait();
-  if (tid >= 128 && tid < 256) {
-    // un-rotated query (fp16 arithmetic as the reference) -> Q operand rows 0..3 (rows 4..15 are
-    // zero); element of pair i (c or d part) sits at the contraction position of the in-place K~
-    // layout: column 8*(i/8) + (i%8)/2 (+4 for the d part), two elements per column
-    const int d = tid - 128, i = d & 63;
-    const int kk = 2 * (8 * (i >> 3) + ((i & 7) >> 1) + (d >= 64 ? 4 : 0)) + (i & 1);
-    const float phase = __fmul_rn((float)sh.pos_q, p.inv_freq[i]);
-    float sn, cs;
-    sincosf(phase, &sn, &cs);
-    const __half c16 = __float2half_rn(cs), s16 = __float2half_rn(sn);
-    const __half* qg = reinterpret_cast<const __half*>(sq.q) + (size_t)kv * GQA * HD;
-    unsigned char* qcol = q_s + (kk >> 6) * 2048 + (kk & 7) * 2;
-#pragma unroll
-    for (int h = 0; h < GQA; ++h) {
-      const __half x = qg[h * HD + d];
-      const __half other = qg[h * HD + (d ^ 64)];
-      const __half rot = (d < 64) ? __hneg(other) : other;
-      const __half un = __hsub(__hmul(x, c16), __hmul(rot, s16));
-      *reinterpret_cast<__half*>(qcol + sw128_off(h, (kk >> 3) & 7)) = un;
-      qr_s[h * HD + d] = __half2float(x);
-    }
-#pragma unroll
-    for (int n = GQA; n < 16; ++n) *reinterpret_cast<__half*>(qcol + sw128_off(n, (kk >> 3) & 7)) = __float2half_rn(0.f);
   }
   fence_proxy_async();
   tc_fence_before();
@@ -347,9 +321,71 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     const int gather_first = gq * 32 + lane;
     const uint2* cbv4 = cbv + (lane & (PP_CB_COPIES - 1));   // this lane's copy of the codebook (fewer bank conflicts)
 
+    // 256 units of (token row, 16 codes) over the 96 threads of the three non-issuing warps;
+    // consecutive lanes take consecutive rows, so the eight 16-byte stores of a quarter-warp fall
+    // into eight different bank groups of the swizzled tile
+    auto gather_tile = [&]() {
+#pragma unroll 1
+      for (int u = gather_first; u < 256; u += 96) {
+        const int row = u & 127, hf = u >> 7;              // codes 16*hf .. 16*hf+15 of the row
+        const uint4 cq = *reinterpret_cast<const uint4*>(vc_g + row * VQ_GROUPS + 16 * hf);
+        const uint32_t cw[4] = {cq.x, cq.y, cq.z, cq.w};
+        unsigned char* dst = v_g + hf * 16384;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          const uint32_t two = cw[jj >> 1] >> (16 * (jj & 1));
+          const uint2 e0 = cbv4[4 * (two & 0xff)], e1 = cbv4[4 * ((two >> 8) & 0xff)];
+          *reinterpret_cast<uint4*>(dst + sw128_off(row, jj)) = make_uint4(e0.x, e0.y, e1.x, e1.y);
+        }
+      }
+    };
+
     bool bad = false;
     if (issuer && g < 2 && g < n_my) bad |= !issue_mma1(g);
     __syncwarp();
+    // the V codes of the group's first tile are cache data as well: expanded while waiting
+    if (g < n_my && quad != issuer_quad) {
+      bad |= !mbar_wait(V_FULL(g), 0u, abort_s);
+      gather_tile();
+    }
+    // Up to here only tensors that no decode call ever writes were touched (weights, coefficients,
+    // V codes, codebooks): the set-up, the first two tiles' unpack and reconstruction products run
+    // while the launch before this one is still finishing.  The query, the new token, the stream
+    // rows, the phase table, the scratch and the output may come from, or still be in use by, that
+    // launch: every role waits for it before it touches them.
+    // The last consumer group -- whose first tile is the furthest away -- stages the query; the
+    // cos / sin of the query position for the thread's pair do not depend on the launch before.
+    __half c16 = __float2half_rn(1.f), s16 = __float2half_rn(0.f);
+    if (g == PP_STAGES - 1) {
+      const float phase = __fmul_rn((float)sh.pos_q, p.inv_freq[(tid - 256) & 63]);
+      float sn, cs;
+      sincosf(phase, &sn, &cs);
+      c16 = __float2half_rn(cs); s16 = __float2half_rn(sn);
+    }
+    griddep_wait();
+    if (g == PP_STAGES - 1) {
+      // un-rotated query (fp16 arithmetic as the reference) -> Q operand rows 0..3 (rows 4..15 are
+      // zero); element of pair i (c or d part) sits at the contraction position of the in-place K~
+      // layout: column 8*(i/8) + (i%8)/2 (+4 for the d part), two elements per column
+      const int d = tid - 256, i = d & 63;
+      const int kk = 2 * (8 * (i >> 3) + ((i & 7) >> 1) + (d >= 64 ? 4 : 0)) + (i & 1);
+      const __half* qg = reinterpret_cast<const __half*>(sq.q) + (size_t)kv * GQA * HD;
+      unsigned char* qcol = q_s + (kk >> 6) * 2048 + (kk & 7) * 2;
+#pragma unroll
+      for (int h = 0; h < GQA; ++h) {
+        const __half x = qg[h * HD + d];
+        const __half other = qg[h * HD + (d ^ 64)];
+        const __half rot = (d < 64) ? __hneg(other) : other;
+        const __half un = __hsub(__hmul(x, c16), __hmul(rot, s16));
+        *reinterpret_cast<__half*>(qcol + sw128_off(h, (kk >> 3) & 7)) = un;
+        qr_s[h * HD + d] = __half2float(x);
+      }
+#pragma unroll
+      for (int n = GQA; n < 16; ++n) *reinterpret_cast<__half*>(qcol + sw128_off(n, (kk >> 3) & 7)) = __float2half_rn(0.f);
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(Q_READY);
+    }
     // Fused append: in the CTA that owns the newest streamed row, two warps of the last consumer
     // group -- whose first tile is the furthest away -- quantise the new token now.  The row is
     // read near the end of the kernel by the unpack warps, which wait on APPEND_DONE first.
@@ -407,6 +443,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       bad = named_bar_or(1 + g, 128, bad || *abort_s);
       if (bad) break;                                   // uniform over the group
       if (issuer) {
+        if (use == 0) bad |= !mbar_wait(Q_READY, 0u, abort_s);
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
@@ -419,25 +456,11 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       // (while the tensor core computes the scores)
       // ---- gather the token's V row (32 codes) into the group's V tile ---------------------------
       // the previous tile's P.V product must have finished reading the V tile and P
-      if (use > 0) bad |= !mbar_wait(O_DONE(g), (uint32_t)((use - 1) & 1), abort_s);
-      bad |= !mbar_wait(V_FULL(g), par, abort_s);
-      if (quad != issuer_quad) {
-        // 256 units of (token row, 16 codes) over 96 threads; consecutive lanes take consecutive rows,
-        // so the eight 16-byte stores of a quarter-warp fall into eight different bank groups of the
-        // swizzled tile
-#pragma unroll 1
-        for (int u = gather_first; u < 256; u += 96) {
-          const int row = u & 127, hf = u >> 7;              // codes 16*hf .. 16*hf+15 of the row
-          const uint4 cq = *reinterpret_cast<const uint4*>(vc_g + row * VQ_GROUPS + 16 * hf);
-          const uint32_t cw[4] = {cq.x, cq.y, cq.z, cq.w};
-          unsigned char* dst = v_g + hf * 16384;
-#pragma unroll
-          for (int jj = 0; jj < 8; ++jj) {
-            const uint32_t two = cw[jj >> 1] >> (16 * (jj & 1));
-            const uint2 e0 = cbv4[4 * (two & 0xff)], e1 = cbv4[4 * ((two >> 8) & 0xff)];
-            *reinterpret_cast<uint4*>(dst + sw128_off(row, jj)) = make_uint4(e0.x, e0.y, e1.x, e1.y);
-          }
-        }
+      // (the first tile's were expanded before the loop)
+      if (use > 0) {
+        bad |= !mbar_wait(O_DONE(g), (uint32_t)((use - 1) & 1), abort_s);
+        bad |= !mbar_wait(V_FULL(g), par, abort_s);
+        if (quad != issuer_quad) gather_tile();
       }
 
       // ---- softmax over this warp's 32 tokens ---------------------------------------------------
@@ -566,11 +589,13 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     // row.  The rows get a record of their own: standard V space, while the middle's record is in rotated space.
     // The coefficient staging buffers are free by now and serve as merge scratch.
     bad = named_bar_or(4, 128, bad || *abort_s);
+    griddep_wait();
     if (!bad && p.n_row_parts > 0) {
-      if (append_here) bad = !mbar_wait(APPEND_DONE, 0u, abort_s);
+      bad = !mbar_wait(Q_READY, 0u, abort_s);
+      if (append_here) bad |= !mbar_wait(APPEND_DONE, 0u, abort_s);
       SoftmaxState st;
       softmax_init(st);
-      process_rows(st, sq, sh, kv, part + p.n_row_parts * quad, p.n_row_parts * 4, qr_s, cbs_s, lane);
+      if (!bad) process_rows(st, sq, sh, kv, part + p.n_row_parts * quad, p.n_row_parts * 4, qr_s, cbs_s, lane);
       float* scratch = reinterpret_cast<float*>(c_s);
       partial_store<4>(st, scratch, quad, lane);
       named_bar_sync(4, 128);
