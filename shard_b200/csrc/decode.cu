@@ -68,7 +68,9 @@ static DecodePlan make_plan(const ShardDecodeShape& sh, int batch) {
       if (pl.n_row_parts > MAX_ROW_CTAS) pl.n_row_parts = MAX_ROW_CTAS;
     }
   }
-  pl.n_parts = pl.n_chunks + pl.n_row_parts;
+  // a chunk CTA folds its share of the rows into its one record; only a launch without a middle
+  // has records of rows alone
+  pl.n_parts = pl.n_chunks > 0 ? pl.n_chunks : pl.n_row_parts;
   pl.grid_x = pl.n_chunks > 0 ? pl.n_chunks : pl.n_row_parts;
   return pl;
 }

@@ -61,8 +61,9 @@ constexpr int PP_MISC_BYTES = 1024 + 1024;   // state + barriers, and slack for 
 __host__ __device__ constexpr int pp_w_bytes(int nw) { return ((32 * nw + 16 + 63) / 64) * 16384; }
 // staging filled by the bulk copy engine: two tiles of packed coefficients (128 rows x R/2 bytes)
 // and one tile of V codes (128 rows x 32 bytes) per consumer group
-// (at least 4224 bytes each, so that the pair can double as the 8.3 KB row-merge scratch)
-__host__ __device__ constexpr int pp_c_bytes(int nw) { return 128 * 16 * nw < 4224 ? 4224 : 128 * 16 * nw; }
+// (at least 5312 bytes each, so that the pair can double as the 8.3 KB row-merge scratch plus the
+// 2.1 KB record of the rows)
+__host__ __device__ constexpr int pp_c_bytes(int nw) { return 128 * 16 * nw < 5312 ? 5312 : 128 * 16 * nw; }
 constexpr int PP_VC_BYTES = 128 * VQ_GROUPS;
 __host__ __device__ constexpr int pp_smem_bytes(int nw) {
   return pp_w_bytes(nw) + PP_STAGES * (PP_V_BYTES + PP_P_BYTES) + PP_Q_BYTES + PP_CB_BYTES + PP_ROWQ_BYTES +
@@ -116,6 +117,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   float* qr_s = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(cbv) + PP_CB_BYTES);   // queries as given [4][128]
   float* cbs_s = qr_s + GQA * HD;                                  // stream codebook [256]
   unsigned char* c_s = reinterpret_cast<unsigned char*>(cbs_s + 256);         // [2] coefficient tiles
+  float* rows_rec_s = reinterpret_cast<float*>(c_s) + 4 * GQA * 130;   // record of this CTA's rows (valid once the coefficient buffers are free)
   unsigned char* vc_s = c_s + 2 * pp_c_bytes(NW);                  // [3] V code tiles
   float* misc = reinterpret_cast<float*>(vc_s + PP_STAGES * PP_VC_BYTES);
   float* alpha_s = misc;                                           // [3][16]
@@ -599,7 +601,41 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       float* scratch = reinterpret_cast<float*>(c_s);
       partial_store<4>(st, scratch, quad, lane);
       named_bar_sync(4, 128);
-      partial_merge<4>(scratch, rec_rows, m);
+      partial_merge<4>(scratch, rows_rec_s, m);
+      // Into the rotated space of the middle's accumulator (normalised Hadamard over the channels of
+      // each head; the combine's inverse transform takes it back): the CTA then has one record.
+      float v[GQA];
+#pragma unroll
+      for (int h = 0; h < GQA; ++h) v[h] = rows_rec_s[h * PART + 4 + m];
+#pragma unroll
+      for (int hh = 1; hh < 32; hh <<= 1) {
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) {
+          const float other = __shfl_xor_sync(0xffffffffu, v[h], hh);
+          v[h] = (m & hh) ? other - v[h] : v[h] + other;
+        }
+      }
+      for (int hh = 32; hh < HD; hh <<= 1) {
+        named_bar_sync(4, 128);
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) rows_rec_s[h * PART + 4 + m] = v[h];
+        named_bar_sync(4, 128);
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) {
+          const float other = rows_rec_s[h * PART + 4 + (m ^ hh)];
+          v[h] = (m & hh) ? other - v[h] : v[h] + other;
+        }
+      }
+      named_bar_sync(4, 128);
+#pragma unroll
+      for (int h = 0; h < GQA; ++h) rows_rec_s[h * PART + 4 + m] = v[h] / SQRT_HD;
+    } else {
+      // no rows for this launch (or gave up): an empty state
+#pragma unroll
+      for (int h = 0; h < GQA; ++h) {
+        if (m == 0) { rows_rec_s[h * PART] = neg_inf(); rows_rec_s[h * PART + 1] = 0.f; }
+        rows_rec_s[h * PART + 4 + m] = 0.f;
+      }
     }
   }
 
@@ -622,7 +658,9 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   {
     // run_m is kept in the log2 domain (score * log2 e); the record carries the natural-log maximum
     const int h = tid >> 7, m = tid & 127;              // 512 threads: one (head, channel) each
-    float M = neg_inf();
+    // the rows' state (natural-log reference, already in rotated space and final units)
+    const float rows_m = rows_rec_s[h * PART] * LOG2E, rows_l = rows_rec_s[h * PART + 1], rows_a = rows_rec_s[h * PART + 4 + m];
+    float M = rows_m;
 #pragma unroll
     for (int e = 0; e < 12; ++e) M = fmaxf(M, m_s[16 * (e >> 2) + 4 * (e & 3) + h]);
     float L = 0.f, a = 0.f;
@@ -634,9 +672,11 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       L = fmaf(wt, l_s[idx], L);
       a = fmaf(wt, reinterpret_cast<const float*>(v_s + (e >> 2) * PP_V_BYTES)[(4 * (e & 3) + h) * HD + m], a);
     }
+    const float wr = (rows_m == neg_inf()) ? 0.f : exp2f(rows_m - M);
+    L = fmaf(wr, rows_l, L);
     float* rec = rec_base + h * PART;
     if (m == 0) { rec[0] = M * LN2; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
-    rec[4 + m] = a * ch_scale;
+    rec[4 + m] = fmaf(wr, rows_a, a * ch_scale);
   }
   if (tid == 0 && *abort_s) {
     // gave up somewhere: do not leave while a bulk copy may still be landing in this CTA's memory
