@@ -222,14 +222,22 @@ __device__ __forceinline__ void partial_merge(const float* scratch, float* __res
 // (`released`: the caller has already issued __threadfence + __syncthreads after those writes).
 // Each takes a ticket; the CTA that draws the last one sees all records of that KV head
 // (release/acquire through the fences around the ticket), merges them for the head's four
-// query heads exactly as decode_combine_kernel does (same order, same operations), and puts
-// the counter back to zero for the next call.  `sm` needs GQA*HD + 2*GQA*n_parts floats that
-// are free; NTHREADS >= GQA*HD.  Thread tid handles head tid/128, channel tid%128.
+// query heads, and puts the counter back to zero for the next call.  The result does not depend
+// on which CTA is last: the parts are always summed in the same order.  `sm` needs 3072 floats
+// (or GQA*HD + 2*GQA*n_parts + 8 for more than 64 parts) that are free; NTHREADS >= 512.
+//
+// The merging CTA is the critical path of the whole launch and runs this code once, out of a
+// cold instruction cache: it is kept short.  Warp w < 16 takes query head w % 4 and the parts
+// p = w / 4 (mod 4), lane = channels 4*lane .. 4*lane+3: one 16-byte load per part and lane, all of
+// a warp's loads in flight together; lane j also fetches (max, sum-exp) of parts j and j + 32, from
+// which the warp derives the weights and hands them round by shuffle.  The four partial sums of a
+// head meet in shared memory; warp h < 4 adds them in order, runs the inverse Hadamard over the
+// 128 channels (two butterflies inside the thread, five by shuffle) and writes the output.
 template <int NTHREADS>
 __device__ __forceinline__ void ticket_combine(const DecodeParams& p, const ShardSeq& sq, int kv, int b,
                                                float* sm_raw, int tid, bool released = false) {
   volatile float* sm = sm_raw;   // exchanged between threads: every access must reach shared memory
-  static_assert(NTHREADS >= GQA * HD, "one thread per (head, channel)");
+  static_assert(NTHREADS >= GQA * HD, "16 merging warps");
   __shared__ int last_s;
   if (!released) {               // the caller has not yet fenced its record writes and synchronised the CTA
     __threadfence();
@@ -244,58 +252,95 @@ __device__ __forceinline__ void ticket_combine(const DecodeParams& p, const Shar
   __syncthreads();
   if (!last_s) return;
   __threadfence();
-  const bool active = tid < GQA * HD;
   const int n_q = p.sh.n_q, n_parts = p.n_parts, n_rot = p.n_chunks;
-  const int hl = (tid >> 7) & (GQA - 1), h = kv * GQA + hl, d = tid & (HD - 1);
+  const int w = tid >> 5, lane = tid & 31;
   const float* base0 = p.ws + ((size_t)b * n_parts * n_q + (size_t)kv * GQA) * PART;
   const size_t pstride = (size_t)n_q * PART;
-  // This CTA is on the critical path of the launch: nobody else is left.
-  float M = neg_inf(), L = 0.f, rot = 0.f, stdv = 0.f;
-  const float* accp = base0 + hl * PART + 4 + d;
+  const bool fin = tid < GQA * 32;                    // warp hl < 4 finishes query head hl
+  float M = neg_inf(), L = 0.f;                       // of head w % 4 (the same in every lane)
+  float o4[4] = {0.f, 0.f, 0.f, 0.f};                 // channels 4*lane .. 4*lane+3 of head w (fin threads)
   if (n_parts <= 64) {
-    // Every load goes out before anything is waited for, so the merge costs one round trip to L2
-    // and no shared memory: lane j of a warp fetches (max, sum-exp) of parts j and j + 32 of the
-    // warp's head -- the same for all its lanes -- and every thread its channel of every part (a
-    // launch over one sequence of a model with 8 KV heads has 36 parts).
-    constexpr int COMBINE_BATCH = 36;
-    const int lane = tid & 31;
-    float a0[COMBINE_BATCH];
+    float rot4[4] = {0.f, 0.f, 0.f, 0.f}, std4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (w < 16) {
+      const int hl = w & 3, sub = w >> 2;
+      const float* rec0 = base0 + hl * PART;
+      constexpr int KB = 5;                            // loads of a batch (18 parts: one batch)
+      float4 a[KB];
 #pragma unroll
-    for (int pi = 0; pi < COMBINE_BATCH; ++pi) a0[pi] = (active && pi < n_parts) ? __ldcg(accp + pi * pstride) : 0.f;
-    float mj[2], lj[2];
+      for (int k = 0; k < KB; ++k) {
+        const int pi = sub + 4 * k;
+        a[k] = pi < n_parts ? __ldcg(reinterpret_cast<const float4*>(rec0 + pi * pstride + 4) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      float mj[2], lj[2], wj[2];
 #pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      const int pj = lane + 32 * k;
-      const float* rec = base0 + pj * pstride + hl * PART;
-      mj[k] = (active && pj < n_parts) ? __ldcg(rec) : neg_inf();
-      lj[k] = (active && pj < n_parts) ? __ldcg(rec + 1) : 0.f;
-    }
-    if (active) {                                      // whole warps: tid < GQA * HD
+      for (int k = 0; k < 2; ++k) {
+        const int pj = lane + 32 * k;
+        mj[k] = pj < n_parts ? __ldcg(rec0 + pj * pstride) : neg_inf();
+        lj[k] = pj < n_parts ? __ldcg(rec0 + pj * pstride + 1) : 0.f;
+      }
       M = warp_max(fmaxf(mj[0], mj[1]));
-      float wj[2];
 #pragma unroll
       for (int k = 0; k < 2; ++k) wj[k] = (mj[k] == neg_inf()) ? 0.f : exp2f((mj[k] - M) * LOG2E);
-      // (parts in ascending order, the same operations as decode_combine_kernel)
+      L = warp_sum(fmaf(wj[0], lj[0], wj[1] * lj[1]));
+      for (int k0 = 0; sub + 4 * k0 < n_parts; k0 += KB) {
+        if (k0 > 0) {
 #pragma unroll
-      for (int pi = 0; pi < COMBINE_BATCH; ++pi) {
-        const float wt = __shfl_sync(0xffffffffu, wj[pi >> 5], pi & 31);
-        const float lp = __shfl_sync(0xffffffffu, lj[pi >> 5], pi & 31);
-        if (pi < n_parts) {
-          L = fmaf(wt, lp, L);
-          if (pi < n_rot) rot = fmaf(wt, a0[pi], rot); else stdv = fmaf(wt, a0[pi], stdv);
+          for (int k = 0; k < KB; ++k) {
+            const int pi = sub + 4 * (k0 + k);
+            a[k] = pi < n_parts ? __ldcg(reinterpret_cast<const float4*>(rec0 + pi * pstride + 4) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < KB; ++k) {
+          const int pi = sub + 4 * (k0 + k);          // the same in every lane of the warp
+          const float wt = __shfl_sync(0xffffffffu, (pi & 32) ? wj[1] : wj[0], pi & 31);
+          if (pi < n_parts) {
+            float* dst = pi < n_rot ? rot4 : std4;
+            dst[0] = fmaf(wt, a[k].x, dst[0]); dst[1] = fmaf(wt, a[k].y, dst[1]);
+            dst[2] = fmaf(wt, a[k].z, dst[2]); dst[3] = fmaf(wt, a[k].w, dst[3]);
+          }
         }
       }
-      for (int pi = COMBINE_BATCH; pi < n_parts; ++pi) {
-        const float wt = __shfl_sync(0xffffffffu, wj[pi >> 5], pi & 31);
-        const float lp = __shfl_sync(0xffffffffu, lj[pi >> 5], pi & 31);
-        const float a = __ldcg(accp + pi * pstride);
-        L = fmaf(wt, lp, L);
-        if (pi < n_rot) rot = fmaf(wt, a, rot); else stdv = fmaf(wt, a, stdv);
+      if (sub > 0) {
+        float4* part4 = reinterpret_cast<float4*>(sm_raw) + ((sub - 1) * GQA + hl) * 64 + lane;
+        part4[0] = make_float4(rot4[0], rot4[1], rot4[2], rot4[3]);
+        part4[32] = make_float4(std4[0], std4[1], std4[2], std4[3]);
       }
     }
+    __syncthreads();
+    if (fin) {
+#pragma unroll
+      for (int sub = 1; sub < 4; ++sub) {
+        const float4* part4 = reinterpret_cast<const float4*>(sm_raw) + ((sub - 1) * GQA + w) * 64 + lane;
+        const float4 r = part4[0], t = part4[32];
+        rot4[0] += r.x; rot4[1] += r.y; rot4[2] += r.z; rot4[3] += r.w;
+        std4[0] += t.x; std4[1] += t.y; std4[2] += t.z; std4[3] += t.w;
+      }
+      if (n_rot > 0) {
+        // inverse (= forward) normalised Hadamard over the 128 channels of the head; channel
+        // d = 4*lane + c: the butterflies of distance 1 and 2 inside the thread, the others by shuffle
+        { const float x0 = rot4[0] + rot4[1], x1 = rot4[0] - rot4[1], x2 = rot4[2] + rot4[3], x3 = rot4[2] - rot4[3];
+          rot4[0] = x0 + x2; rot4[1] = x1 + x3; rot4[2] = x0 - x2; rot4[3] = x1 - x3; }
+#pragma unroll
+        for (int hh = 1; hh < 32; hh <<= 1) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const float other = __shfl_xor_sync(0xffffffffu, rot4[c], hh);
+            rot4[c] = (lane & hh) ? other - rot4[c] : rot4[c] + other;
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) rot4[c] = rot4[c] / SQRT_HD;
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) o4[c] = rot4[c] + std4[c];
+    }
   } else {
-    // many parts: (max, sum-exp) of every part of the four heads staged in shared memory
-    volatile float* ms = sm + GQA * HD;                 // [GQA][n_parts]
+    // many parts: thread = (head tid / 128, channel tid % 128), (max, sum-exp) of every part of the
+    // four heads staged in shared memory, the result handed to the finishing threads through it
+    const bool active = tid < GQA * HD;
+    const int hl = (tid >> 7) & (GQA - 1), d = tid & (HD - 1);
+    volatile float* ms = sm + GQA * HD + 8;             // [GQA][n_parts]
     volatile float* ls = ms + GQA * n_parts;            // [GQA][n_parts]
     for (int idx = tid; idx < GQA * n_parts; idx += NTHREADS) {
       const int hh = idx / n_parts, pi = idx - hh * n_parts;
@@ -304,41 +349,46 @@ __device__ __forceinline__ void ticket_combine(const DecodeParams& p, const Shar
       ls[idx] = __ldcg(rec + 1);
     }
     __syncthreads();
+    float Mh = neg_inf(), Lh = 0.f, rot = 0.f, stdv = 0.f;
     if (active) {
-      for (int pi = 0; pi < n_parts; ++pi) M = fmaxf(M, ms[hl * n_parts + pi]);
-#pragma unroll 12
+      for (int pi = 0; pi < n_parts; ++pi) Mh = fmaxf(Mh, ms[hl * n_parts + pi]);
+      const float* accp = base0 + hl * PART + 4 + d;
+#pragma unroll 4
       for (int pi = 0; pi < n_parts; ++pi) {
         const float a = __ldcg(accp + pi * pstride);
         const float m = ms[hl * n_parts + pi];
-        const float wt = (m == neg_inf()) ? 0.f : exp2f((m - M) * LOG2E);
-        L = fmaf(wt, ls[hl * n_parts + pi], L);
+        const float wt = (m == neg_inf()) ? 0.f : exp2f((m - Mh) * LOG2E);
+        Lh = fmaf(wt, ls[hl * n_parts + pi], Lh);
         if (pi < n_rot) rot = fmaf(wt, a, rot); else stdv = fmaf(wt, a, stdv);
       }
     }
-  }
-  // inverse (= forward) normalised Hadamard of the rotated-space sum over the 128 channels of a
-  // head (four warps): the butterflies inside a warp by shuffle, the last two through shared memory
-  float v = rot;
-  if (n_rot > 0) {
+    float v = rot;
+    if (n_rot > 0) {
+      for (int hh = 1; hh < HD; hh <<= 1) {
+        if (active) sm[tid] = v;
+        __syncthreads();
+        if (active) {
+          const float other = sm[tid ^ hh];
+          v = (d & hh) ? other - v : v + other;
+        }
+        __syncthreads();
+      }
+      v = v / SQRT_HD;
+    }
     if (active) {
+      sm[tid] = v + stdv;
+      if (d == 0) { sm[GQA * HD + hl] = Mh; sm[GQA * HD + GQA + hl] = Lh; }
+    }
+    __syncthreads();
+    if (fin) {
 #pragma unroll
-      for (int hh = 1; hh < 32; hh <<= 1) {
-        const float other = __shfl_xor_sync(0xffffffffu, v, hh);
-        v = (d & hh) ? other - v : v + other;
-      }
+      for (int c = 0; c < 4; ++c) o4[c] = sm[w * HD + 4 * lane + c];
+      M = sm[GQA * HD + w];
+      L = sm[GQA * HD + GQA + w];
     }
-    for (int hh = 32; hh < HD; hh <<= 1) {
-      if (active) sm[tid] = v;
-      __syncthreads();
-      if (active) {
-        const float other = sm[tid ^ hh];
-        v = (d & hh) ? other - v : v + other;
-      }
-      __syncthreads();
-    }
-    v = v / SQRT_HD;
   }
-  const float o = v + stdv;
+  const int h = kv * GQA + w;                          // query head of a finishing thread
+  const float4 o = make_float4(o4[0], o4[1], o4[2], o4[3]), ml = make_float4(M, L, 0.f, 0.f);
   if (p.push.world > 0) {
     // Sequence-split decode: this CTA holds the rank's final record of four query heads.  It goes
     // straight into slot epoch % 2 of EVERY rank's exchange buffer (plain peer stores over
@@ -348,12 +398,12 @@ __device__ __forceinline__ void ticket_combine(const DecodeParams& p, const Shar
     const int slot = (int)(p.push.epoch & 1u);
     const size_t flag_bytes = peer_flag_bytes(p.push.world, p.sh.nkv);
     const size_t slot_floats = peer_slot_floats(p.push.world, p.sh.nkv);
-    if (active) {
+    if (fin) {
       for (int r = 0; r < p.push.world; ++r) {
-        float* rec = reinterpret_cast<float*>(p.push.bufs[r] + flag_bytes) + slot * slot_floats +
-                     ((size_t)p.push.rank * n_q + h) * PART;
-        if (d == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
-        rec[4 + d] = o;
+        float4* rec = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.push.bufs[r] + flag_bytes) + slot * slot_floats +
+                                                ((size_t)p.push.rank * n_q + h) * PART);
+        if (lane == 0) rec[0] = ml;
+        rec[1 + lane] = o;
       }
     }
     __threadfence_system();
@@ -378,20 +428,25 @@ __device__ __forceinline__ void ticket_combine(const DecodeParams& p, const Shar
       __syncthreads();
       if (last_s) {
         if (tid == 0 && p.push.status) atomicExch(p.push.status, 1);
-      } else if (active) {
-        reinterpret_cast<__half*>(p.push.merged_out)[(size_t)h * HD + d] =
-            merge_rank_records(p.push.bufs[p.push.rank], p.push.world, p.sh.nkv, slot, h, d);
+      } else if (tid < GQA * HD) {
+        const int hq = kv * GQA + (tid >> 7), d = tid & (HD - 1);
+        reinterpret_cast<__half*>(p.push.merged_out)[(size_t)hq * HD + d] =
+            merge_rank_records(p.push.bufs[p.push.rank], p.push.world, p.sh.nkv, slot, hq, d);
       }
     }
     if (!sq.out) return;
   }
-  if (!active) return;
+  if (!fin) return;
   if (p.sh.partial_out) {
-    float* rec = reinterpret_cast<float*>(sq.out) + (size_t)h * PART;
-    if (d == 0) { rec[0] = M; rec[1] = L; rec[2] = 0.f; rec[3] = 0.f; }
-    rec[4 + d] = o;
+    float4* rec = reinterpret_cast<float4*>(reinterpret_cast<float*>(sq.out) + (size_t)h * PART);
+    if (lane == 0) rec[0] = ml;
+    rec[1 + lane] = o;
   } else {
-    reinterpret_cast<__half*>(sq.out)[(size_t)h * HD + d] = __float2half_rn(o / L);
+    const __half2 lo = __floats2half2_rn(o4[0] / L, o4[1] / L), hi = __floats2half2_rn(o4[2] / L, o4[3] / L);
+    uint2 pk;
+    pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+    reinterpret_cast<uint2*>(reinterpret_cast<__half*>(sq.out) + (size_t)h * HD)[lane] = pk;
   }
 }
 

@@ -690,7 +690,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   tc_fence_before();
   __syncthreads();
   if (warp == PP_UNPACK_WARP0) tmem_dealloc(tmem_base, PP_TMEM_COLS);
-  ticket_combine<PP_THREADS>(p, sq, kv, blockIdx.z, reinterpret_cast<float*>(w_s), tid, true);
+  ticket_combine<PP_THREADS>(p, sq, kv, blockIdx.z, reinterpret_cast<float*>(v_s), tid, true);   // the V tiles are free
 }
 
 // Prepared weights: per KV head, W = basis * coefficient scale as fp16 in the K-major, 128-byte
