@@ -22,8 +22,8 @@
 //                       per-warp online softmax -> P
 //                       MMA3  O[128 ch x 16]     = V^T . P^T         (V, P in smem)
 //                       and every thread rescales-and-accumulates its output channel
-//   append              the CTA that owns the newest streamed row quantises the new token in the
-//                       start-up slack of the last consumer group
+//   append              in the CTA that owns the newest streamed row two warps of the last consumer
+//                       group quantise the new token while its other two stage the query
 //   combine             the last CTA of a (sequence, KV head) to finish merges all records
 //
 // Tensor memory: two key stages of 128 columns (tile t uses stage t % 2: un-rotated keys in fp32,
@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     *mma1_next = 0;
     for (int j = 0; j < 3; ++j) mbar_init(A_FULL(j), 4);
     mbar_init(APPEND_DONE, 2);
-    mbar_init(Q_READY, 4);
+    mbar_init(Q_READY, 2);
     *abort_s = 0;
     fence_mbar_init();
   }
@@ -355,44 +355,51 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     // while the launch before this one is still finishing.  The query, the new token, the stream
     // rows, the phase table, the scratch and the output may come from, or still be in use by, that
     // launch: every role waits for it before it touches them.
-    // The last consumer group -- whose first tile is the furthest away -- stages the query; the
-    // cos / sin of the query position for the thread's pair do not depend on the launch before.
+    // The last consumer group -- whose first tile is the furthest away -- has two jobs here: its
+    // first two warps stage the query (the cos / sin of the query position do not depend on the
+    // launch before), and in the CTA that owns the newest streamed row its other two quantise the
+    // new token into it meanwhile (bit-identical to stream_quantize_kernel).  The row is read near
+    // the end of the kernel by the unpack warps, which wait on APPEND_DONE first.
+    const bool stages_q = g == PP_STAGES - 1 && quad < 2;
     __half c16 = __float2half_rn(1.f), s16 = __float2half_rn(0.f);
-    if (g == PP_STAGES - 1) {
-      const float phase = __fmul_rn((float)sh.pos_q, p.inv_freq[(tid - 256) & 63]);
+    if (stages_q) {
+      const float phase = __fmul_rn((float)sh.pos_q, p.inv_freq[tid - 256]);
       float sn, cs;
       sincosf(phase, &sn, &cs);
       c16 = __float2half_rn(cs); s16 = __float2half_rn(sn);
     }
     griddep_wait();
-    if (g == PP_STAGES - 1) {
+    if (stages_q) {
       // un-rotated query (fp16 arithmetic as the reference) -> Q operand rows 0..3 (rows 4..15 are
       // zero); element of pair i (c or d part) sits at the contraction position of the in-place K~
-      // layout: column 8*(i/8) + (i%8)/2 (+4 for the d part), two elements per column
-      const int d = tid - 256, i = d & 63;
-      const int kk = 2 * (8 * (i >> 3) + ((i & 7) >> 1) + (d >= 64 ? 4 : 0)) + (i & 1);
+      // layout: column 8*(i/8) + (i%8)/2 (+4 for the d part), two elements per column.  This thread
+      // takes pair i: dimensions i and i + 64.
+      const int i = tid - 256;
       const __half* qg = reinterpret_cast<const __half*>(sq.q) + (size_t)kv * GQA * HD;
-      unsigned char* qcol = q_s + (kk >> 6) * 2048 + (kk & 7) * 2;
+      __half x_lo[GQA], x_hi[GQA];
 #pragma unroll
-      for (int h = 0; h < GQA; ++h) {
-        const __half x = qg[h * HD + d];
-        const __half other = qg[h * HD + (d ^ 64)];
-        const __half rot = (d < 64) ? __hneg(other) : other;
-        const __half un = __hsub(__hmul(x, c16), __hmul(rot, s16));
-        *reinterpret_cast<__half*>(qcol + sw128_off(h, (kk >> 3) & 7)) = un;
-        qr_s[h * HD + d] = __half2float(x);
+      for (int h = 0; h < GQA; ++h) { x_lo[h] = qg[h * HD + i]; x_hi[h] = qg[h * HD + i + 64]; }
+#pragma unroll
+      for (int part2 = 0; part2 < 2; ++part2) {
+        const int d = i + 64 * part2;
+        const int kk = 2 * (8 * (i >> 3) + ((i & 7) >> 1) + (part2 ? 4 : 0)) + (i & 1);
+        unsigned char* qcol = q_s + (kk >> 6) * 2048 + (kk & 7) * 2;
+#pragma unroll
+        for (int h = 0; h < GQA; ++h) {
+          const __half x = part2 ? x_hi[h] : x_lo[h];
+          const __half rot = part2 ? x_lo[h] : __hneg(x_hi[h]);
+          const __half un = __hsub(__hmul(x, c16), __hmul(rot, s16));
+          *reinterpret_cast<__half*>(qcol + sw128_off(h, (kk >> 3) & 7)) = un;
+          qr_s[h * HD + d] = __half2float(x);
+        }
+#pragma unroll
+        for (int n = GQA; n < 16; ++n) *reinterpret_cast<__half*>(qcol + sw128_off(n, (kk >> 3) & 7)) = __float2half_rn(0.f);
       }
-#pragma unroll
-      for (int n = GQA; n < 16; ++n) *reinterpret_cast<__half*>(qcol + sw128_off(n, (kk >> 3) & 7)) = __float2half_rn(0.f);
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(Q_READY);
-    }
-    // Fused append: in the CTA that owns the newest streamed row, two warps of the last consumer
-    // group -- whose first tile is the furthest away -- quantise the new token now.  The row is
-    // read near the end of the kernel by the unpack warps, which wait on APPEND_DONE first.
-    if (append_here && g == PP_STAGES - 1 && quad < 2) {
-      append_new_token(sq, sh, kv, cbs_s, quad == 1, lane);
+    } else if (append_here && g == PP_STAGES - 1) {
+      append_new_token(sq, sh, kv, cbs_s, quad == 3, lane);
       __syncwarp();
       if (lane == 0) mbar_arrive(APPEND_DONE);
     }
