@@ -57,25 +57,6 @@ __device__ __forceinline__ void softmax_init(SoftmaxState& st) {
   }
 }
 
-// one streamed token: fp16 value of channels 4*lane..+3 exactly as the reference's
-// dequantize_per_token + norm scaling produce it
-__device__ __forceinline__ void stream_dequant_lane4(const uint8_t* __restrict__ idx_row, float nrm,
-                                                     const float* __restrict__ cbs, const float4 sg, int lane,
-                                                     float (&o)[4]) {
-  // L2-coherent load: the row may have been written by this CTA a moment ago (fused append)
-  const uint32_t codes = __ldcg(reinterpret_cast<const unsigned int*>(idx_row + 4 * lane));
-  float x[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) x[i] = cbs[(codes >> (8 * i)) & 0xff];
-  fwht128_lane4(x, lane);
-  const float sgn[4] = {sg.x, sg.y, sg.z, sg.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __half unit = __float2half_rn(__fmul_rn(__fdiv_rn(x[i], SQRT_HD), sgn[i]));
-    o[i] = __half2float(__float2half_rn(__fmul_rn(__half2float(unit), nrm)));
-  }
-}
-
 // online-softmax update with one token whose 4 scores are warp-uniform
 __device__ __forceinline__ void row_update(SoftmaxState& st, const float (&s)[GQA], const float (&v)[4]) {
 #pragma unroll
@@ -133,45 +114,84 @@ __device__ __forceinline__ void process_rows(SoftmaxState& st, const ShardSeq& s
                                              const float* __restrict__ qr, const float* __restrict__ cbs, int lane) {
   const int n_sw = sh.n_sink + sh.n_win, n_fp = n_sw + sh.n_dec, n_rows = n_fp + sh.n_stream;
   if (u_first >= n_rows) return;
-  float4 sg = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (sh.n_stream > 0) sg = *reinterpret_cast<const float4*>(sq.signs + 4 * lane);
   float4 qv[GQA];
 #pragma unroll
   for (int h = 0; h < GQA; ++h) qv[h] = *reinterpret_cast<const float4*>(qr + h * HD + 4 * lane);
-  for (int u = u_first; u < n_rows; u += u_step) {
-    float kx[4], vx[4];
-    if (u < n_fp) {
-      const bool in_sink = u < sh.n_sink, in_dec = u >= n_sw;
-      const int r = in_sink ? u : (in_dec ? u - n_sw : u - sh.n_sink);
-      const int rows = in_sink ? sh.n_sink : (in_dec ? (sh.dec_cap > 0 ? sh.dec_cap : sh.n_dec) : sh.n_win);
-      const __half* kb = reinterpret_cast<const __half*>(in_sink ? sq.sink_k : (in_dec ? sq.dec_k : sq.win_k));
-      const __half* vb = reinterpret_cast<const __half*>(in_sink ? sq.sink_v : (in_dec ? sq.dec_v : sq.win_v));
-      const size_t off = ((size_t)kv * rows + r) * HD + 4 * lane;
-      const uint2 kr = *reinterpret_cast<const uint2*>(kb + off);
-      const uint2 vr = *reinterpret_cast<const uint2*>(vb + off);
-      const float2 k01 = __half22float2(*reinterpret_cast<const __half2*>(&kr.x));
-      const float2 k23 = __half22float2(*reinterpret_cast<const __half2*>(&kr.y));
-      const float2 v01 = __half22float2(*reinterpret_cast<const __half2*>(&vr.x));
-      const float2 v23 = __half22float2(*reinterpret_cast<const __half2*>(&vr.y));
-      kx[0] = k01.x; kx[1] = k01.y; kx[2] = k23.x; kx[3] = k23.y;
-      vx[0] = v01.x; vx[1] = v01.y; vx[2] = v23.x; vx[3] = v23.y;
-    } else {
-      const size_t row = (size_t)(u - n_fp) * sh.nkv + kv;
-      const float kn = __half2float(__ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(sq.st_k_norm) + row)));
-      const float vn = __half2float(__ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(sq.st_v_norm) + row)));
-      stream_dequant_lane4(sq.st_k_idx + row * HD, kn, cbs, sg, lane, kx);
-      stream_dequant_lane4(sq.st_v_idx + row * HD, vn, cbs, sg, lane, vx);
-    }
+  auto attend = [&](const float (&kx)[4], const float (&vx)[4]) {
     float s[GQA];
 #pragma unroll
     for (int h = 0; h < GQA; ++h) {
       float d = qv[h].x * kx[0];
       d = fmaf(qv[h].y, kx[1], d);
       d = fmaf(qv[h].z, kx[2], d);
-      d = fmaf(qv[h].w, kx[3], d);
-      s[h] = warp_sum(d) * INV_SQRT_HD;
+      s[h] = fmaf(qv[h].w, kx[3], d);
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int h = 0; h < GQA; ++h) s[h] += __shfl_xor_sync(0xffffffffu, s[h], o);   // four reductions side by side
+    }
+#pragma unroll
+    for (int h = 0; h < GQA; ++h) s[h] *= INV_SQRT_HD;
     row_update(st, s, vx);
+  };
+  // ---- fp16 rows: sink, window, fp16 decode buffer ---------------------------------------------
+  int u = u_first;
+  for (; u < n_fp; u += u_step) {
+    const bool in_sink = u < sh.n_sink, in_dec = u >= n_sw;
+    const int r = in_sink ? u : (in_dec ? u - n_sw : u - sh.n_sink);
+    const int rows = in_sink ? sh.n_sink : (in_dec ? (sh.dec_cap > 0 ? sh.dec_cap : sh.n_dec) : sh.n_win);
+    const __half* kb = reinterpret_cast<const __half*>(in_sink ? sq.sink_k : (in_dec ? sq.dec_k : sq.win_k));
+    const __half* vb = reinterpret_cast<const __half*>(in_sink ? sq.sink_v : (in_dec ? sq.dec_v : sq.win_v));
+    const size_t off = ((size_t)kv * rows + r) * HD + 4 * lane;
+    const uint2 kr = *reinterpret_cast<const uint2*>(kb + off);
+    const uint2 vr = *reinterpret_cast<const uint2*>(vb + off);
+    const float2 k01 = __half22float2(*reinterpret_cast<const __half2*>(&kr.x));
+    const float2 k23 = __half22float2(*reinterpret_cast<const __half2*>(&kr.y));
+    const float2 v01 = __half22float2(*reinterpret_cast<const __half2*>(&vr.x));
+    const float2 v23 = __half22float2(*reinterpret_cast<const __half2*>(&vr.y));
+    const float kx[4] = {k01.x, k01.y, k23.x, k23.y}, vx[4] = {v01.x, v01.y, v23.x, v23.y};
+    attend(kx, vx);
+  }
+  // ---- streamed rows (u is this warp's first row behind the fp16 rows) ---------------------------
+  if (u >= n_rows) return;
+  const float4 sg = *reinterpret_cast<const float4*>(sq.signs + 4 * lane);
+  const float sgn[4] = {sg.x, sg.y, sg.z, sg.w};
+  // L2-coherent loads: a row may have been written by this CTA a moment ago (fused append).  The
+  // next row's codes and norms are fetched while the current row is worked on.
+  auto fetch = [&](int ur, uint32_t& kc, uint32_t& vc, unsigned short& kn16, unsigned short& vn16) {
+    const size_t row = (size_t)(ur - n_fp) * sh.nkv + kv;
+    kn16 = __ldcg(reinterpret_cast<const unsigned short*>(sq.st_k_norm) + row);
+    vn16 = __ldcg(reinterpret_cast<const unsigned short*>(sq.st_v_norm) + row);
+    kc = __ldcg(reinterpret_cast<const unsigned int*>(sq.st_k_idx + row * HD + 4 * lane));
+    vc = __ldcg(reinterpret_cast<const unsigned int*>(sq.st_v_idx + row * HD + 4 * lane));
+  };
+  uint32_t kc_next = 0u, vc_next = 0u;
+  unsigned short kn_next = 0, vn_next = 0;
+  fetch(u, kc_next, vc_next, kn_next, vn_next);
+  for (; u < n_rows; u += u_step) {
+    const uint32_t kc = kc_next, vc = vc_next;
+    const float kn = __half2float(__ushort_as_half(kn_next)), vn = __half2float(__ushort_as_half(vn_next));
+    if (u + u_step < n_rows) fetch(u + u_step, kc_next, vc_next, kn_next, vn_next);
+    // fp16 value of channels 4*lane..+3 exactly as the reference's dequantize_per_token + norm
+    // scaling produce it
+    float xk[4], xv[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      xk[i] = cbs[(kc >> (8 * i)) & 0xff];
+      xv[i] = cbs[(vc >> (8 * i)) & 0xff];
+    }
+    fwht128_lane4(xk, lane);
+    fwht128_lane4(xv, lane);
+    float kx[4], vx[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __half ku = __float2half_rn(__fmul_rn(__fdiv_rn(xk[i], SQRT_HD), sgn[i]));
+      const __half vu = __float2half_rn(__fmul_rn(__fdiv_rn(xv[i], SQRT_HD), sgn[i]));
+      kx[i] = __half2float(__float2half_rn(__fmul_rn(__half2float(ku), kn)));
+      vx[i] = __half2float(__float2half_rn(__fmul_rn(__half2float(vu), vn)));
+    }
+    attend(kx, vx);
   }
 }
 
