@@ -99,6 +99,42 @@ __device__ __forceinline__ bool named_bar_or(int id, int count, bool flag) {
 }
 
 
+// A launch without a middle segment (a cache that holds fp16 and streamed rows only): every CTA
+// attends to its share of the rows (row u belongs to CTA u % gridDim.x, one warp per row), the CTA
+// that owns the newest streamed row quantises it first, the last CTA of a KV head combines.
+constexpr int ROWS_THREADS = 512;
+constexpr int ROWS_SMEM_BYTES = (2 * GQA * HD + 256 + (ROWS_THREADS / 32) * GQA * 130) * 4;
+__global__ void __launch_bounds__(ROWS_THREADS, 1) decode_rows_only_kernel(const __grid_constant__ DecodeParams p) {
+  extern __shared__ __align__(128) unsigned char smem_rows[];
+  const ShardSeq& sq = p.table ? p.table[blockIdx.z] : p.one;
+  const ShardDecodeShape& sh = p.sh;
+  const int kv = blockIdx.y, part = blockIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_rows = sh.n_sink + sh.n_win + sh.n_dec + sh.n_stream;
+  const bool append_here = sh.append && p.n_row_parts > 0 && (n_rows - 1) % p.n_row_parts == part;
+  float* rec_rows = p.ws + (((size_t)blockIdx.z * p.n_parts + part) * sh.n_q + (size_t)kv * GQA) * PART;
+  griddep_launch();
+  griddep_wait();
+  float* qn = reinterpret_cast<float*>(smem_rows);
+  float* qr = qn + GQA * HD;
+  float* cbs = qr + GQA * HD;
+  float* scratch = cbs + 256;
+  if (sh.n_stream > 0) for (int i = tid; i < 256; i += ROWS_THREADS) cbs[i] = p.codebook[i];
+  if (tid < HD) stage_query(sq, kv, sh.pos_q, p.inv_freq, tid, qn, qr);
+  __syncthreads();
+  if (append_here) {
+    if (warp < 2) append_new_token(sq, sh, kv, cbs, warp == 1, lane);
+    __syncthreads();
+  }
+  SoftmaxState st;
+  softmax_init(st);
+  process_rows(st, sq, sh, kv, part + p.n_row_parts * warp, p.n_row_parts * (ROWS_THREADS / 32), qr, cbs, lane);
+  partial_store<ROWS_THREADS / 32>(st, scratch, warp, lane);
+  __syncthreads();
+  if (tid < HD) partial_merge<ROWS_THREADS / 32>(scratch, rec_rows, tid);
+  ticket_combine<ROWS_THREADS>(p, sq, kv, blockIdx.z, scratch, tid);
+}
+
 template <int NW>  // rank / 32
 __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(const __grid_constant__ DecodeParams p) {
   constexpr int R = NW * 32;
@@ -139,32 +175,8 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   const int n_rows = sh.n_sink + sh.n_win + sh.n_dec + sh.n_stream;
   // the CTA that owns the newest streamed row quantises it before anybody reads the stream
   const bool append_here = sh.append && p.n_row_parts > 0 && (n_rows - 1) % p.n_row_parts == part;
-  float* rec_rows = p.ws + (((size_t)blockIdx.z * p.n_parts + p.n_chunks + part) * sh.n_q + (size_t)kv * GQA) * PART;
 
   griddep_launch();
-  if (p.n_chunks == 0) {
-    // a launch without a middle segment: every CTA only attends to its share of the rows
-    griddep_wait();
-    float* qn = reinterpret_cast<float*>(smem);
-    float* qr = qn + GQA * HD;
-    float* cbs = qr + GQA * HD;
-    float* scratch = cbs + 256;
-    if (sh.n_stream > 0) for (int i = tid; i < 256; i += PP_THREADS) cbs[i] = p.codebook[i];
-    if (tid < HD) stage_query(sq, kv, sh.pos_q, p.inv_freq, tid, qn, qr);
-    __syncthreads();
-    if (append_here) {
-      if (warp < 2) append_new_token(sq, sh, kv, cbs, warp == 1, lane);
-      __syncthreads();
-    }
-    SoftmaxState st;
-    softmax_init(st);
-    process_rows(st, sq, sh, kv, part + p.n_row_parts * warp, p.n_row_parts * PP_WARPS, qr, cbs, lane);
-    partial_store<PP_WARPS>(st, scratch, warp, lane);
-    __syncthreads();
-    if (tid < HD) partial_merge<PP_WARPS>(scratch, rec_rows, tid);
-    ticket_combine<PP_THREADS>(p, sq, kv, blockIdx.z, scratch, tid);
-    return;
-  }
 
   // barrier addresses
   const uint32_t bar0 = smem_u32(bars);
@@ -743,7 +755,6 @@ int launch_prepare_pipe(const void* basis, const void* cscale, const void* mean,
 template <int NW>
 static int launch_pipe_one(const DecodeParams& p, dim3 grid, cudaStream_t st) {
   constexpr int SMEM = pp_smem_bytes(NW);
-  static_assert(SMEM >= (2 * GQA * HD + 256 + PP_WARPS * GQA * 130) * 4, "row path scratch must fit");
   // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel
   static std::atomic<bool> configured[MAX_DEVICES];
   int dev = -1;
@@ -780,7 +791,16 @@ static int launch_pipe_one(const DecodeParams& p, dim3 grid, cudaStream_t st) {
   return e == cudaSuccess ? 0 : (int)e;
 }
 
+static int launch_rows_only(const DecodeParams& p, dim3 grid, cudaStream_t st) {
+  // (38 KB of dynamic shared memory: no opt-in needed)
+  static_assert(ROWS_SMEM_BYTES <= 48 * 1024, "fits the default dynamic shared memory");
+  decode_rows_only_kernel<<<grid, ROWS_THREADS, ROWS_SMEM_BYTES, st>>>(p);
+  const cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : (int)e;
+}
+
 int launch_partial_pipe(const DecodeParams& p, dim3 grid, cudaStream_t st) {
+  if (p.n_chunks == 0) return launch_rows_only(p, grid, st);
   switch (p.sh.rank / 32) {
     case 1: return launch_pipe_one<1>(p, grid, st);
     case 2: return launch_pipe_one<2>(p, grid, st);

@@ -416,6 +416,21 @@ def test_decode_odd_rank_is_padded():
     assert layer._gpu_compressed["k_rank_kernel"] == 192 and "k_coeffs_padded" in layer._gpu_compressed
 
 
+def test_decode_two_kv_heads_many_records():
+    """A geometry with 2 KV heads: 74 CTAs per head on a 148-SM device, i.e. more records per
+    head than the combine's register path takes (64) -- its shared-memory path runs."""
+    from gpu_helpers import FakeCache, FakeLayer, gc_to_device, random_gc, random_query
+    nkv, n_comp = 2, 12000
+    gc_np = random_gc(n_comp, rank=192, nkv=nkv, n_sink=4, n_win=64, seed=21)
+    inv = O.default_inv_freq()
+    layer = FakeLayer(gc_to_device(gc_np, nkv=nkv), FakeCache(torch.from_numpy(inv), nkv=nkv))
+    q = random_query(n_q=4 * nkv, seed=22)
+    out = _decode(layer, q, n_comp + 100)
+    exact, *_ = O.attention_exact(q, gc_np, n_comp + 100, inv, nkv=nkv)
+    assert np.isfinite(out).all()
+    assert tol_ok(out, exact, atol=EXACT_ATOL, rtol=EXACT_RTOL), np.abs(out - exact).max()
+
+
 def test_decode_far_positions():
     """Query 131072 tokens past the window start: fp32 phase products of ~1e5 rad."""
     _check_random(700, 192, 4, 64, pos_q=131072 + 700, compress_start=4, seed=4, atol=2e-3, rtol=1e-2)
