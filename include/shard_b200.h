@@ -156,8 +156,8 @@ size_t shard_b200_decode_workspace_bytes(const ShardDecodeShape* shape_host, int
  * (read it with shard_b200_decode_status).
  * The kernel is launched with programmatic stream serialization: its CTAs may start while the
  * kernel directly in front of it in the stream is still running, and before waiting for that
- * kernel they read k_wprep, k_coeffs, v_indices, v_centroids, the stream codebook and (batch > 1)
- * the ShardSeq table.  So the kernel directly in front must not be one that WRITES any of those
+ * kernel they read k_wprep, k_coeffs, v_indices, v_centroids, the stream codebook, inv_freq and
+ * (batch > 1) the ShardSeq table, and already expand the first tiles of the middle segment from them.  So the kernel directly in front must not be one that WRITES any of those
  * (shard_b200_decode_prepare, the kernels that produce the codes, a copy into the table): for
  * the first decode call behind such work set shape.no_overlap = 1, which launches the plain way
  * (or set SHARD_B200_PDL=0 in the environment to do so always).  Everything else -- query, new
