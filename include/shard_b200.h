@@ -157,11 +157,14 @@ size_t shard_b200_decode_workspace_bytes(const ShardDecodeShape* shape_host, int
  * The kernel is launched with programmatic stream serialization: its CTAs may start while the
  * kernel directly in front of it in the stream is still running, and before waiting for that
  * kernel they read k_wprep, k_coeffs, v_indices, v_centroids, the stream codebook, inv_freq and
- * (batch > 1) the ShardSeq table, and already expand the first tiles of the middle segment from them.  So the kernel directly in front must not be one that WRITES any of those
+ * (batch > 1) the ShardSeq table, and already expand the first tiles of the middle segment from them;
+ * they also read the phase table, which therefore has to be complete when the launch starts (it is
+ * when shard_b200_phase_table produced it earlier on the same stream: that kernel does not release
+ * the launches behind it early).  So the kernel directly in front must not be one that WRITES any of those
  * (shard_b200_decode_prepare, the kernels that produce the codes, a copy into the table): for
  * the first decode call behind such work set shape.no_overlap = 1, which launches the plain way
  * (or set SHARD_B200_PDL=0 in the environment to do so always).  Everything else -- query, new
- * token, stream rows, phase table, workspace, output -- is read and written only after the
+ * token, stream rows, workspace, output -- is read and written only after the
  * preceding work has completed.
  */
 int shard_b200_decode_attn(const ShardSeq* seqs, int32_t batch, const ShardDecodeShape* shape_host,

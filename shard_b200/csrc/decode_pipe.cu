@@ -365,8 +365,10 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     // Up to here only tensors that no decode call ever writes were touched (weights, coefficients,
     // V codes, codebooks): the set-up, the first two tiles' unpack and reconstruction products run
     // while the launch before this one is still finishing.  The query, the new token, the stream
-    // rows, the phase table, the scratch and the output may come from, or still be in use by, that
-    // launch: every role waits for it before it touches them.
+    // rows, the scratch and the output may come from, or still be in use by, that launch: every
+    // role waits for it before it touches them.  (The phase table is complete before any CTA of this
+    // launch starts: the kernel that writes it never releases its dependents early.  So the first
+    // two groups also rotate their first tile before they wait.)
     // The last consumer group -- whose first tile is the furthest away -- has two jobs here: its
     // first two warps stage the query (the cos / sin of the query position do not depend on the
     // launch before), and in the CTA that owns the newest streamed row its other two quantise the
@@ -380,7 +382,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       sincosf(phase, &sn, &cs);
       c16 = __float2half_rn(cs); s16 = __float2half_rn(sn);
     }
-    griddep_wait();
+    if (g == PP_STAGES - 1) griddep_wait();
     if (stages_q) {
       // un-rotated query (fp16 arithmetic as the reference) -> Q operand rows 0..3 (rows 4..15 are
       // zero); element of pair i (c or d part) sits at the contraction position of the in-place K~
@@ -463,6 +465,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       tc_fence_before();
       bad = named_bar_or(1 + g, 128, bad || *abort_s);
       if (bad) break;                                   // uniform over the group
+      if (use == 0) griddep_wait();                     // (the last group has waited already)
       if (issuer) {
         if (use == 0) bad |= !mbar_wait(Q_READY, 0u, abort_s);
         tc_fence_after();
@@ -549,6 +552,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
       }
       __syncwarp();
     }
+    griddep_wait();                                     // a group without tiles, or one that gave up early
     // the group's accumulated P.V: channel m, 16 (warp, head) columns
     if (use > 0 && !(bad || *abort_s)) {
       bad |= !mbar_wait(O_DONE(g), (uint32_t)((use - 1) & 1), abort_s);
