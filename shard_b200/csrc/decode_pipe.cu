@@ -253,9 +253,10 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   else if (tid >= 32 && tid < 128 && sh.n_stream > 0)
     for (int i = tid - 32; i < 256; i += 96) cbs_s[i] = p.codebook[i];
   {
-    // P rows that a token's warp does not own stay zero for the whole kernel
+    // P rows that a token's warp does not own stay zero for the whole kernel, and so do rows 4..15
+    // of the Q operand (it follows the P operands in memory)
     uint4* z = reinterpret_cast<uint4*>(p_s);
-    for (int i = tid; i < (PP_STAGES * PP_P_BYTES) / 16; i += PP_THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = tid; i < (PP_STAGES * PP_P_BYTES + PP_Q_BYTES) / 16; i += PP_THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
   }
   fence_proxy_async();
   tc_fence_before();
@@ -384,7 +385,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     }
     if (g == PP_STAGES - 1) griddep_wait();
     if (stages_q) {
-      // un-rotated query (fp16 arithmetic as the reference) -> Q operand rows 0..3 (rows 4..15 are
+      // un-rotated query (fp16 arithmetic as the reference) -> Q operand rows 0..3 (rows 4..15 stay
       // zero); element of pair i (c or d part) sits at the contraction position of the in-place K~
       // layout: column 8*(i/8) + (i%8)/2 (+4 for the d part), two elements per column.  This thread
       // takes pair i: dimensions i and i + 64.
@@ -406,8 +407,6 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
           *reinterpret_cast<__half*>(qcol + sw128_off(h, (kk >> 3) & 7)) = un;
           qr_s[h * HD + d] = __half2float(x);
         }
-#pragma unroll
-        for (int n = GQA; n < 16; ++n) *reinterpret_cast<__half*>(qcol + sw128_off(n, (kk >> 3) & 7)) = __float2half_rn(0.f);
       }
       fence_proxy_async();
       __syncwarp();
