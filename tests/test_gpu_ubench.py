@@ -38,5 +38,11 @@ def test_tcgen05_mma_cycle_table(tmp_path):
     assert rows["m128 n128 TS (A in tensor memory)"][1] >= 40            # the issuing thread is held at the pipe's rate
     assert 45 <= rows["m128 n16 TS"][0] <= 75
     assert rows["m128 n16 TS, two accumulators alternating"][0] >= 0.8 * rows["m128 n16 TS"][0]
-    tile = [v for k, v in rows.items() if k.startswith("one decode tile")][0]
+    tile = rows["one decode tile: 13 x n128 + 8 x n16 TS + 8 x n16 SS"]
     assert 1200 <= tile[0] <= 2200
+    # the same with the P.V operand laid out as the kernel's V tile, alone and beside other warps'
+    # shared-memory traffic: traffic can only slow the tensor path down
+    tile_mn = rows["one decode tile, P.V operand MN-major as in the kernel"]
+    heavy = rows["one decode tile (MN-major) + 15 warps of heavy shared-memory traffic"]
+    assert 1200 <= tile_mn[0] <= 3000
+    assert heavy[0] >= 0.95 * tile_mn[0]

@@ -43,24 +43,26 @@ __device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr, uint32_t lbo, uin
   return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) |
          ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
-__host__ __device__ constexpr uint32_t mk_idesc(int M, int N) {
-  return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+__host__ __device__ constexpr uint32_t mk_idesc(int M, int N, bool a_mn_major = false) {
+  return (1u << 4) | ((a_mn_major ? 1u : 0u) << 15) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 enum Case {
-  N128_SS, N128_TS, N128_TS_LD, N64_TS, N16_SS, N16_TS, N16_TS_TWO_ACC, M64_N128_SS, M64_N16_SS, TILE_MIX, N_CASES
+  N128_SS, N128_TS, N128_TS_LD, N64_TS, N16_SS, N16_TS, N16_TS_TWO_ACC, M64_N128_SS, M64_N16_SS, TILE_MIX,
+  TILE_MIX_MN, TILE_MIX_MN_SMEM_LIGHT, TILE_MIX_MN_SMEM_HEAVY, N_CASES
 };
 
-// out[0]: cycles until the group has completed, out[1]: cycles the issuing thread spent issuing
+// out[0]: cycles until the group has completed, out[1]: cycles the issuing thread spent issuing,
+// out[2]: 16-byte shared-memory loads + stores per lane done by the other warps meanwhile
 template <int which>
-__global__ void __launch_bounds__(128) bench(int reps, long long* out) {
+__global__ void __launch_bounds__(512) bench(int reps, long long* out) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ uint32_t slot;
   __shared__ uint64_t bar;
   __shared__ volatile int stop;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  for (int i = tid; i < 128 * 1024 / 4; i += 128) reinterpret_cast<uint32_t*>(smem)[i] = 0x3c003c00u;
+  for (int i = tid; i < 128 * 1024 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(smem)[i] = 0x3c003c00u;
   if (tid == 0) { mbar_init(smem_u32(&bar), 1); stop = 0; }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&slot)), "r"(512) : "memory");
@@ -77,13 +79,16 @@ __global__ void __launch_bounds__(128) bench(int reps, long long* out) {
   bool timed_out = false;
   uint32_t parity = 0;
   const bool load_warps = which == N128_TS_LD;
+  constexpr bool tile_mix = which == TILE_MIX || which >= TILE_MIX_MN;
+  constexpr bool smem_warps = which == TILE_MIX_MN_SMEM_LIGHT || which == TILE_MIX_MN_SMEM_HEAVY;
+  const uint64_t ad_mn = desc_sw128(a_u, 16384, 1024);   // A as the decode kernel's V tile: MN-major, two 16 KB halves
   if (warp == 0) {
     for (int r = 0; r < reps && !timed_out; ++r) {
       const long long t0 = clock64();
       if (lane == 0) {
 #pragma unroll 1
         for (int rr = 0; rr < 4; ++rr) {
-          if (which == TILE_MIX) {
+          if (tile_mix) {
             // one tile of the decode kernel: 13 k-steps of 128 columns, then 8 + 8 of 16 columns
 #pragma unroll
             for (int k = 0; k < 13; ++k)
@@ -93,8 +98,8 @@ __global__ void __launch_bounds__(128) bench(int reps, long long* out) {
               umma_ts(tb + 128, tb + 8 * k, bd + (uint64_t)(((k >> 2) * 2048u + (k & 3) * 32u) >> 4), mk_idesc(128, 16), k > 0);
 #pragma unroll
             for (int k = 0; k < 8; ++k)
-              umma_ss(tb + 160, ad + (uint64_t)((k * 2048u) >> 4), bd + (uint64_t)(((k >> 2) * 2048u + (k & 3) * 32u) >> 4),
-                      mk_idesc(128, 16), k > 0);
+              umma_ss(tb + 160, (which == TILE_MIX ? ad : ad_mn) + (uint64_t)((k * 2048u) >> 4),
+                      bd + (uint64_t)(((k >> 2) * 2048u + (k & 3) * 32u) >> 4), mk_idesc(128, 16, which != TILE_MIX), k > 0);
           } else {
 #pragma unroll
             for (int k = 0; k < 12; ++k) {
@@ -124,7 +129,7 @@ __global__ void __launch_bounds__(128) bench(int reps, long long* out) {
     }
     if (lane == 0) stop = 1;
     if (lane == 0 && blockIdx.x == 0) { out[0] = timed_out ? -1 : t_total; out[1] = t_issue; }
-  } else if (load_warps) {
+  } else if (load_warps && warp < 4) {
     // keep tensor memory busy: every warp reads 16 columns of its lane quarter over and over
     uint32_t acc = 0;
     const uint32_t taddr = tb + 128 + ((uint32_t)(warp * 32) << 16);
@@ -138,6 +143,29 @@ __global__ void __launch_bounds__(128) bench(int reps, long long* out) {
       acc ^= r[0] ^ r[15];
     }
     if (acc == 0x12345678u) out[3] = acc;
+  } else if (smem_warps) {
+    // keep the shared-memory pipe busy the way the decode kernel's V expansion does: every lane
+    // loads and stores 16 bytes of a scratch area (2 KB per warp, inside the B operand: only the
+    // timing matters), with idle arithmetic in between in the light case
+    uint4* scratch = reinterpret_cast<uint4*>(smem + 128 * 1024 - 15 * 2048) + (warp - 1) * 128;
+    uint4 v = make_uint4(tid, 0u, 0u, 0u);
+    long long n = 0;
+    for (int i = 0; i < 4000000 && !stop; ++i) {
+      uint4 x[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) x[j] = scratch[((i + j) * 32 + lane) & 127];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { v.x ^= x[j].x; v.y += x[j].y; }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) scratch[((i + j + 2) * 32 + lane) & 127] = v;
+      n += 8;
+      if (which == TILE_MIX_MN_SMEM_LIGHT) {
+#pragma unroll 1
+        for (int j = 0; j < 48; ++j) v.z = v.z * 1664525u + 1013904223u;
+      }
+    }
+    if (lane == 0 && blockIdx.x == 0) atomicAdd(reinterpret_cast<unsigned long long*>(out + 2), (unsigned long long)n);
+    if (v.z == 0x12345678u) out[3] = v.x;
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -147,7 +175,9 @@ __global__ void __launch_bounds__(128) bench(int reps, long long* out) {
 template <int C>
 void launch_one(int reps, long long* d) {
   cudaFuncSetAttribute(bench<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 130 * 1024);
-  bench<C><<<148, 128, 130 * 1024>>>(reps, d);
+  // the cases with shared-memory traffic run 15 traffic warps beside the issuing warp
+  const int threads = (C == TILE_MIX_MN_SMEM_LIGHT || C == TILE_MIX_MN_SMEM_HEAVY) ? 512 : 128;
+  bench<C><<<148, threads, 130 * 1024>>>(reps, d);
 }
 void launch(int c, int reps, long long* d) {
   switch (c) {
@@ -160,6 +190,9 @@ void launch(int c, int reps, long long* d) {
     case N16_TS_TWO_ACC: launch_one<N16_TS_TWO_ACC>(reps, d); break;
     case M64_N128_SS: launch_one<M64_N128_SS>(reps, d); break;
     case M64_N16_SS: launch_one<M64_N16_SS>(reps, d); break;
+    case TILE_MIX_MN: launch_one<TILE_MIX_MN>(reps, d); break;
+    case TILE_MIX_MN_SMEM_LIGHT: launch_one<TILE_MIX_MN_SMEM_LIGHT>(reps, d); break;
+    case TILE_MIX_MN_SMEM_HEAVY: launch_one<TILE_MIX_MN_SMEM_HEAVY>(reps, d); break;
     default: launch_one<TILE_MIX>(reps, d); break;
   }
 }
@@ -168,24 +201,31 @@ int main() {
   const char* names[N_CASES] = {
       "m128 n128 SS", "m128 n128 TS (A in tensor memory)", "m128 n128 TS + 3 warps of tcgen05.ld", "m128 n64 TS",
       "m128 n16 SS", "m128 n16 TS", "m128 n16 TS, two accumulators alternating", "m64 n128 SS", "m64 n16 SS",
-      "one decode tile: 13 x n128 + 8 x n16 TS + 8 x n16 SS"};
+      "one decode tile: 13 x n128 + 8 x n16 TS + 8 x n16 SS",
+      "one decode tile, P.V operand MN-major as in the kernel",
+      "one decode tile (MN-major) + 15 warps of light shared-memory traffic",
+      "one decode tile (MN-major) + 15 warps of heavy shared-memory traffic"};
   long long* d;
   if (cudaMalloc(&d, 64) != cudaSuccess) { printf("no CUDA device\n"); return 2; }
   int bad = 0;
   for (int c = 0; c < N_CASES; ++c) {
-    const int reps = 20, per_rep = c == TILE_MIX ? 4 * 29 : 48;
+    const int reps = 20, per_rep = c >= TILE_MIX ? 4 * 29 : 48;
     cudaMemset(d, 0, 64);
     launch(c, reps, d);
     cudaError_t e = cudaDeviceSynchronize();
-    long long h[2] = {0, 0};
-    cudaMemcpy(h, d, 16, cudaMemcpyDeviceToHost);
+    long long h[3] = {0, 0, 0};
+    cudaMemcpy(h, d, 24, cudaMemcpyDeviceToHost);
     if (e != cudaSuccess || h[0] < 0) {
       printf("%-56s: %s\n", names[c], e != cudaSuccess ? cudaGetErrorString(e) : "timeout");
       bad = 1;
       if (e != cudaSuccess) break;
       continue;
     }
-    if (c == TILE_MIX)
+    if (c >= TILE_MIX_MN_SMEM_LIGHT)
+      // a 16-byte access per lane is 4 wavefronts per warp instruction; the traffic warps' totals over the measured time
+      printf("%-56s: %8.1f cycles per tile until complete, %8.1f cycles of the issuing thread, %.2f load/store wavefronts per cycle\n",
+             names[c], h[0] / (double)reps / 4, h[1] / (double)reps / 4, 4.0 * h[2] / (double)h[0]);
+    else if (c >= TILE_MIX)
       printf("%-56s: %8.1f cycles per tile until complete, %8.1f cycles of the issuing thread\n", names[c],
              h[0] / (double)reps / 4, h[1] / (double)reps / 4);
     else
