@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
              V_FULL(g));
   };
 
-  // ---- one-time setup: every warp does its share, one CTA barrier at the end ---------------------
+  // ---- one-time set-up, first part: tensor memory, mbarriers, the first bulk copies ---------------
   if (warp == PP_UNPACK_WARP0) {
     tmem_alloc(smem_u32(tmem_slot), PP_TMEM_COLS);
     tmem_relinquish();
@@ -245,20 +245,7 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
     *abort_s = 0;
     fence_mbar_init();
   }
-  if (tid >= 256) {
-    const uint2 e = reinterpret_cast<const uint2*>(sq.v_centroids)[tid - 256];
-#pragma unroll
-    for (int c = 0; c < PP_CB_COPIES; ++c) cbv[PP_CB_COPIES * (tid - 256) + c] = e;
-  }
-  else if (tid >= 32 && tid < 128 && sh.n_stream > 0)
-    for (int i = tid - 32; i < 256; i += 96) cbs_s[i] = p.codebook[i];
-  {
-    // P rows that a token's warp does not own stay zero for the whole kernel, and so do rows 4..15
-    // of the Q operand (it follows the P operands in memory)
-    uint4* z = reinterpret_cast<uint4*>(p_s);
-    for (int i = tid; i < (PP_STAGES * PP_P_BYTES + PP_Q_BYTES) / 16; i += PP_THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
-  }
-  fence_proxy_async();
+  // (one CTA barrier for what everybody needs: tensor memory, the mbarriers, the copies in flight)
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -274,6 +261,23 @@ __global__ void __launch_bounds__(PP_THREADS, 1) decode_partial_pipe_kernel(cons
   if (warp < PP_CONS_WARPS) {
     // =============================== consumer groups ======================================
     const int g = warp >> 2, quad = warp & 3, m = quad * 32 + lane;
+    // Second part of the set-up, by the consumer warps alone -- the unpack warps are already at
+    // work on the first tile: the codebooks into shared memory, zeros where they have to stay.
+    if (tid < 256) {
+      const uint2 e = reinterpret_cast<const uint2*>(sq.v_centroids)[tid];
+#pragma unroll
+      for (int c = 0; c < PP_CB_COPIES; ++c) cbv[PP_CB_COPIES * tid + c] = e;
+    } else if (sh.n_stream > 0) {
+      for (int i = tid - 256; i < 256; i += 128) cbs_s[i] = p.codebook[i];
+    }
+    {
+      // P rows that a token's warp does not own stay zero for the whole kernel, and so do rows 4..15
+      // of the Q operand (it follows the P operands in memory)
+      uint4* z = reinterpret_cast<uint4*>(p_s);
+      for (int i = tid; i < (PP_STAGES * PP_P_BYTES + PP_Q_BYTES) / 16; i += PP_CONS_WARPS * 32) z[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_proxy_async();
+    named_bar_sync(5, PP_CONS_WARPS * 32);
     // the MMA-issuing threads of the CTA (one per consumer group + the unpack side's) sit on four
     // different warp schedulers: group g issues from its warp g + 1, the unpack side from warp 12
     const int issuer_quad = g + 1;
