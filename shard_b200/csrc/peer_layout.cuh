@@ -52,15 +52,27 @@ __device__ __forceinline__ __half merge_rank_records(const unsigned char* own_bu
   const float* base = reinterpret_cast<const float*>(own_buf + peer_flag_bytes(world, nkv)) +
                       slot * peer_slot_floats(world, nkv) + (size_t)h * PART;
   const size_t pstride = (size_t)n_q * PART;
-  float M = neg_inf();
-  for (int r = 0; r < world; ++r) M = fmaxf(M, __ldcg(base + r * pstride));
-  float L = 0.f, acc = 0.f;
-  for (int r = 0; r < world; ++r) {
+  // every rank's (max, sum-exp, channel) goes out as one batch of loads: one round trip instead of
+  // one per rank
+  float m[PEER_MAX_WORLD], l[PEER_MAX_WORLD], a[PEER_MAX_WORLD];
+#pragma unroll
+  for (int r = 0; r < PEER_MAX_WORLD; ++r) {
     const float* rec = base + r * pstride;
-    const float m = __ldcg(rec);
-    const float wt = (m == neg_inf()) ? 0.f : exp2f((m - M) * LOG2E);
-    L = fmaf(wt, __ldcg(rec + 1), L);
-    acc = fmaf(wt, __ldcg(rec + 4 + d), acc);
+    m[r] = r < world ? __ldcg(rec) : neg_inf();
+    l[r] = r < world ? __ldcg(rec + 1) : 0.f;
+    a[r] = r < world ? __ldcg(rec + 4 + d) : 0.f;
+  }
+  float M = neg_inf();
+#pragma unroll
+  for (int r = 0; r < PEER_MAX_WORLD; ++r) M = fmaxf(M, m[r]);
+  float L = 0.f, acc = 0.f;
+#pragma unroll
+  for (int r = 0; r < PEER_MAX_WORLD; ++r) {
+    if (r < world) {
+      const float wt = (m[r] == neg_inf()) ? 0.f : exp2f((m[r] - M) * LOG2E);
+      L = fmaf(wt, l[r], L);
+      acc = fmaf(wt, a[r], acc);
+    }
   }
   return __float2half_rn(acc / L);
 }
