@@ -567,6 +567,49 @@ def test_batched_decoder_matches_single(ops, codebook):
                 assert tol_ok(out[li, s], exact, atol=EXACT_ATOL, rtol=EXACT_RTOL)
 
 
+def test_back_to_back_steps_equal_synchronised_steps(ops, codebook):
+    """The decode kernel starts its set-up and its first tiles while the launch in front is still
+    running.  Steps queued without any synchronisation (query, new token and phase table changing
+    from step to step) must give bit for bit what the same steps give with the device idle
+    before each of them."""
+    from gpu_helpers import FakeCache, FakeLayer, gc_to_device, random_gc
+    from shard_b200.parallel import BatchedDecoder
+
+    class C(FakeCache):
+        _num_layers = 4
+
+    inv = torch.from_numpy(O.default_inv_freq())
+    n_comp, n_steps = 4000, 5
+
+    def make():
+        c = C(inv)
+        c.layers = [FakeLayer(gc_to_device(random_gc(n_comp, seed=300 + li)), c, li) for li in range(4)]
+        return BatchedDecoder([c], stream_capacity=16)
+
+    rng = np.random.default_rng(17)
+    bd_a, bd_b = make(), make()
+    qs = [T(rng.standard_normal(tuple(bd_a.q.shape)).astype(np.float16)) for _ in range(n_steps)]
+    ks = [T(rng.standard_normal(tuple(bd_a.new_k.shape)).astype(np.float16)) for _ in range(n_steps)]
+    vs = [T(rng.standard_normal(tuple(bd_a.new_v.shape)).astype(np.float16)) for _ in range(n_steps)]
+
+    def run(bd, synchronise):
+        outs = []
+        for i in range(n_steps):
+            bd.q.copy_(qs[i]); bd.new_k.copy_(ks[i]); bd.new_v.copy_(vs[i])
+            outs.append(bd.step(n_comp + 68 + i).clone())
+            if synchronise:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        bd.check()
+        return [N(o) for o in outs]
+
+    ref = run(bd_a, True)
+    got = run(bd_b, False)
+    for i in range(n_steps):
+        assert np.isfinite(got[i].astype(np.float32)).all()
+        assert np.array_equal(got[i], ref[i]), f"step {i} differs when the launches overlap"
+
+
 # ------------------------------------------------------------------ Cache end to end
 def test_cache_compress_and_decode_end_to_end(ops):
     """Prefill -> compress() -> streamed decode steps through the public classes."""
