@@ -11,20 +11,26 @@
 //   unpack warps (4)    coefficient rows -> fp16 A operand in tensor memory (one A slot, handed back
 //                       by MMA1 in thirds so that the next tile's unpack overlaps its later k-steps);
 //                       in their slack at the end: this CTA's share of the fp16 sink / window rows
-//                       and the streamed rows (dequantised on the fly), as a record of its own
-//   consumer groups (3 x 4 warps; group g owns stage g and tiles g, g+3, ...), thread = token row;
-//                       one thread per group issues all tensor-core work of the group:
+//                       and the streamed rows (dequantised on the fly), transformed into the rotated
+//                       space of the middle's accumulator and handed to the epilogue
+//   consumer groups (3 x 4 warps; group g owns V / P slot g and tiles g, g+3, ...), thread = token
+//                       row; one thread per group issues all tensor-core work of the group:
 //                       MMA1  K_n[128 tok x 128] = A . W^T           (A from TMEM, W in smem; the last
-//                             k-step adds the mean)
+//                             k-step adds the mean), for the tile two ahead
 //                       K_n -> half2 -> rotate by the relative phase -> K~ written in place
 //                       MMA2  S[128 tok x 16]    = K~ . Q^T          (A = K~ from TMEM)
 //                       meanwhile the token's 32 VQ codes are expanded into the group's V tile
-//                       per-warp online softmax -> P
-//                       MMA3  O[128 ch x 16]     = V^T . P^T         (V, P in smem)
-//                       and every thread rescales-and-accumulates its output channel
+//                       per-warp online softmax with a lazily moving reference point -> P
+//                       MMA3  O[128 ch x 16]    += V^T . P^T         (V, P in smem; accumulates in
+//                             tensor memory, rescaled only when a reference point moved)
 //   append              in the CTA that owns the newest streamed row two warps of the last consumer
 //                       group quantise the new token while its other two stage the query
+//   epilogue            the 12 token-warps' states and the rows' state merge into ONE record per CTA
 //   combine             the last CTA of a (sequence, KV head) to finish merges all records
+//
+// Launched with programmatic stream serialization: the set-up, the first tiles' unpack,
+// reconstruction products, rotation and V expansion use only tensors that no decode call writes
+// (and the phase table, complete before a launch can start) and run before griddepcontrol.wait.
 //
 // Tensor memory: two key stages of 128 columns (tile t uses stage t % 2: un-rotated keys in fp32,
 // overwritten in place by K~ as fp16x2 in columns 0-63 of the stage), the A operand at [256, 360),
